@@ -6,6 +6,9 @@ group of layers, and slots for per-request state of fixed size.
   head_dim] for keys and for values), a free list, and a block table per request.  Groups that keep
   only a window of keys give a page back as soon as every position in it is behind the window of
   all tokens still to come.
+* A mixer may keep several things (pages for one of its branches, a state for another): its spec
+  is then a tuple, every member is placed in its own group as above, and the run's binding holds
+  one binding per member (``CacheBinding.parts``).
 * A *slot* is a small integer that a live request holds from admission to release.  Block-table
   rows on the device and every fixed-size state tensor ([layers, slots, *shape]) are indexed by it;
   a state row is zeroed at admission.  An architecture without such state still gets a slot.
@@ -108,7 +111,7 @@ class _PagedGroup:
     entries: list[int]                        # plan entries that own a layer here, in order
     pool: PagePool
     k: torch.Tensor                           # [layers, pages, kv_heads, page, head_dim]
-    v: torch.Tensor
+    v: torch.Tensor                           # the same with the values' size
     host_table: torch.Tensor                  # int32 [slots, max_pages], pinned when possible
     device_table: torch.Tensor
     tables: dict[str, list[int]] = field(default_factory=dict)   # logical page -> id or -1
@@ -151,9 +154,7 @@ class CacheManager:
         self._where: list[tuple[str, int, int] | None] = [None] * len(cache_specs)
         pin = self.device.type == "cuda"
 
-        for index, spec in enumerate(cache_specs):
-            if spec is None:
-                continue
+        def place(index: int, spec):
             if isinstance(spec, PagedKVSpec):
                 group = next((g for g in self.paged if g.spec == spec), None)
                 if group is None:
@@ -163,22 +164,30 @@ class CacheManager:
                     group = _PagedGroup(spec, [], PagePool(num_pages), None, None, host,
                                         torch.full_like(host, -1, device=self.device))
                     self.paged.append(group)
-                self._where[index] = ("paged", self.paged.index(group), len(group.entries))
+                where = ("paged", self.paged.index(group), len(group.entries))
                 group.entries.append(index)
-            elif isinstance(spec, StateSpec):
-                group = next((g for g in self.states if g.spec == spec), None)
-                if group is None:
-                    group = _StateGroup(spec, [], None)
-                    self.states.append(group)
-                self._where[index] = ("state", self.states.index(group), len(group.entries))
-                group.entries.append(index)
+                return where
+            if isinstance(spec, StateSpec):
+                sgroup = next((g for g in self.states if g.spec == spec), None)
+                if sgroup is None:
+                    sgroup = _StateGroup(spec, [], None)
+                    self.states.append(sgroup)
+                where = ("state", self.states.index(sgroup), len(sgroup.entries))
+                sgroup.entries.append(index)
+                return where
+            raise TypeError(f"plan entry {index}: unknown cache spec {spec!r}")
+
+        for index, spec in enumerate(cache_specs):
+            if spec is None:
+                continue
+            if isinstance(spec, tuple):
+                self._where[index] = ("parts", [place(index, member) for member in spec])
             else:
-                raise TypeError(f"plan entry {index}: unknown cache spec {spec!r}")
+                self._where[index] = place(index, spec)
         for group in self.paged:
-            shape = (len(group.entries), num_pages, group.spec.kv_heads, page_size,
-                     group.spec.head_dim)
-            group.k = torch.zeros(shape, dtype=dtype, device=self.device)
-            group.v = torch.zeros(shape, dtype=dtype, device=self.device)
+            shape = (len(group.entries), num_pages, group.spec.kv_heads, page_size)
+            group.k = torch.zeros((*shape, group.spec.head_dim), dtype=dtype, device=self.device)
+            group.v = torch.zeros((*shape, group.spec.v_dim), dtype=dtype, device=self.device)
             if self.poison:
                 group.k.fill_(float("nan"))
                 group.v.fill_(float("nan"))
@@ -198,10 +207,11 @@ class CacheManager:
         """Bytes that one page index costs over all paged groups (keys and values)."""
         size = torch.empty((), dtype=dtype).element_size()
         groups: dict[PagedKVSpec, int] = {}
-        for spec in cache_specs:
-            if isinstance(spec, PagedKVSpec):
-                groups[spec] = groups.get(spec, 0) + 1
-        return sum(2 * layers * spec.kv_heads * page_size * spec.head_dim * size
+        for entry in cache_specs:
+            for spec in (entry if isinstance(entry, tuple) else (entry,)):
+                if isinstance(spec, PagedKVSpec):
+                    groups[spec] = groups.get(spec, 0) + 1
+        return sum(layers * spec.kv_heads * page_size * (spec.head_dim + spec.v_dim) * size
                    for spec, layers in groups.items())
 
     @property
@@ -246,9 +256,13 @@ class CacheManager:
 
     def _first_needed(self, group: _PagedGroup, length: int) -> int:
         """First logical page that a token at position >= length can still read."""
-        if group.spec.window is None:
-            return 0
-        return max(0, length - group.spec.window + 1) // self.page_size
+        first = 0
+        if group.spec.window is not None:
+            first = max(0, length - group.spec.window + 1)
+        if group.spec.chunk is not None:
+            # the token at `length` reads from the start of its chunk; later ones from later chunks
+            first = max(first, length // group.spec.chunk * group.spec.chunk)
+        return first // self.page_size
 
     def _missing(self, group: _PagedGroup, request_id: str, old_len: int,
                  new_len: int) -> list[int]:
@@ -259,7 +273,7 @@ class CacheManager:
             # the new positions lie in the page that holds the last position: it is held, and so
             # is everything before it unless a window's first page was given back
             if (table and table[(new_len - 1) // self.page_size] >= 0
-                    and (group.spec.window is None or table[min(first, len(table) - 1)] >= 0)):
+                    and (not group.spec.releases or table[min(first, len(table) - 1)] >= 0)):
                 return []
         last = (new_len + self.page_size - 1) // self.page_size
         return [p for p in range(first, last) if p >= len(table) or table[p] < 0]
@@ -329,7 +343,7 @@ class CacheManager:
     def _pass_window(self, request_id: str, live: _Live) -> None:
         new_len = live.length
         for group in self.paged:
-            if group.spec.window is None:
+            if not group.spec.releases:
                 continue
             table = group.tables[request_id]
             first = min(self._first_needed(group, new_len), len(table))
@@ -432,15 +446,21 @@ class CacheManager:
                 source, writes = self._where[self._reads[index]], False
             if source is None:
                 out.append(None)
-                continue
-            kind, g, layer = source
-            if kind == "paged":
-                group = self.paged[g]
-                out.append(CacheBinding("paged", writes, group.k[layer], group.v[layer],
-                                        group.device_table, self.page_size, group.spec.window))
+            elif source[0] == "parts":
+                out.append(CacheBinding("parts", writes,
+                                        parts=[self._binding(member, writes)
+                                               for member in source[1]]))
             else:
-                out.append(CacheBinding("state", writes, state=self.states[g].state[layer]))
+                out.append(self._binding(source, writes))
         return out
+
+    def _binding(self, source, writes: bool) -> CacheBinding:
+        kind, g, layer = source
+        if kind == "paged":
+            group = self.paged[g]
+            return CacheBinding("paged", writes, group.k[layer], group.v[layer],
+                                group.device_table, self.page_size, group.spec.window)
+        return CacheBinding("state", writes, state=self.states[g].state[layer])
 
     # ------------------------------------------------------------------ checks (tests)
     def check_invariants(self) -> None:

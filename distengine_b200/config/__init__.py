@@ -1,6 +1,7 @@
 from .engine import EngineConfig, parse_dtype
 from .llama import LlamaConfig
+from .vomotar import VomotarConfig
 from .model import ConfigError, LayerSpec, ModelConfig, PartSpec, PlanEntry
 
-__all__ = ["EngineConfig", "parse_dtype", "LlamaConfig", "ConfigError", "LayerSpec",
+__all__ = ["EngineConfig", "parse_dtype", "LlamaConfig", "VomotarConfig", "ConfigError", "LayerSpec",
            "ModelConfig", "PartSpec", "PlanEntry"]

@@ -47,10 +47,12 @@ class PartSpec:
 class LayerSpec:
     block: str                      # arrangement kind, e.g. "prenorm"
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: "PartSpec | None"  # None: the layer has a mixer only (and no second norm)
     norm: PartSpec                  # built twice: before the mixer and before the feed-forward
     # where this layer's tensors live in the weight file: part role -> name prefix
     prefixes: tuple[tuple[str, str], ...] = ()
+    # the norm before the feed-forward, where it is not the same as ``norm`` (another tensor name)
+    feed_forward_norm: "PartSpec | None" = None
 
     def prefix(self, role: str) -> str:
         return dict(self.prefixes)[role]

@@ -1,0 +1,232 @@
+// Softmax attention inside chunks of positions, over the paged cache, with a penalty that grows
+// with the logarithm of the distance, keys and values of different sizes, and values that are
+// cached normalised.  Float32 arithmetic on the CUDA cores for float32 or bfloat16 storage:
+// scores, the penalty, the softmax weights and the weighted sum of the values are all 32-bit.
+//
+//   score(i, j) = (q_i . k_j) * scale - r1[h] * log(1 + r2[h] * (i - j))
+//   token i sees key j when j <= i and floor(i / chunk) = floor(j / chunk)   (chunks of positions
+//   counted from 0 of the sequence, whatever portion of it a step brings)
+//
+// A row is (token, query head within its kv head's group); a block takes a tile of 8 rows of one
+// sequence and one kv head, a warp a row, a lane a key of the current tile of 32 keys.  Tiles of
+// keys lie at absolute multiples of 32 and a row walks the tiles of its chunk in ascending order,
+// so a row's result does not depend, bit for bit, on what shares its tile, its step or its batch.
+// The host's work items are those of the other attention kernels (kernels/attention_plan.py),
+// unsplit: a chunk bounds every key range.
+
+#include "common.cuh"
+
+DE_DEFINE_PDL_SWITCH
+
+namespace {
+
+constexpr int ROWS = 8;
+constexpr int TILE = 32;
+constexpr int MAX_D = 256;
+
+struct WorkItem {
+    int seq, row0, kv_begin, kv_end, partial, pad0, pad1, pad2;
+};
+
+// k copied, v divided by its root mean square over the head (eps inside the root), both into the
+// pages.  proj row = [... | k (G dk) | v (G dv)] from column k_col on.  grid (tokens, kv heads).
+template <typename T>
+__global__ void kv_write_normed_kernel(const T* __restrict__ proj, int ld, int k_col,
+                                       const int* __restrict__ positions,
+                                       const int* __restrict__ token_slot, int G, int dk, int dv,
+                                       float eps, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                       const int* __restrict__ block_table, int table_stride,
+                                       int page, int num_pages, int* __restrict__ status) {
+    __shared__ float scratch[33];
+    const int n = blockIdx.x, hk = blockIdx.y;
+    const int pos = positions[n], slot = token_slot[n];
+    pdl_wait();
+    const int page_id = block_table[(size_t)slot * table_stride + pos / page];
+    const T* ks = proj + (size_t)n * ld + k_col + hk * dk;
+    const T* vs = proj + (size_t)n * ld + k_col + G * dk + hk * dv;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dv; i += blockDim.x) {
+        const float x = to_float(vs[i]);
+        ss = fmaf(x, x, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dv + eps);
+    pdl_trigger();
+    if (page_id < 0 || page_id >= num_pages) {       // never written outside the pool
+        if (threadIdx.x == 0) atomicExch(status, 1);
+        return;
+    }
+    const size_t at = ((size_t)page_id * G + hk) * page + (size_t)(pos % page);
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) k_pages[at * dk + i] = ks[i];
+    for (int i = threadIdx.x; i < dv; i += blockDim.x)
+        v_pages[at * dv + i] = from_float<T>(to_float(vs[i]) * inv);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(ROWS * 32)
+attn_chunk_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                  const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                  const int* __restrict__ block_table, int table_stride, int num_pages,
+                  const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
+                  const int* __restrict__ seq_qlen, const int* __restrict__ seq_pos0,
+                  const WorkItem* __restrict__ items, const float* __restrict__ r1,
+                  const float* __restrict__ r2, int heads, int kv_heads, int dk, int dv, int page,
+                  float scale, int chunk, int* __restrict__ status) {
+    extern __shared__ float smem[];
+    float* Ks = smem;                       // [TILE][dk + 1]; column dk: 0, or -inf without a page
+    float* Vs = Ks + TILE * (dk + 1);       // [TILE][dv]
+    float* Qs = Vs + TILE * dv;             // [ROWS][dk]
+
+    const WorkItem it = items[blockIdx.x];
+    if (it.kv_begin >= it.kv_end) {
+        pdl_wait();
+        return;
+    }
+    const int hk = blockIdx.y;
+    const int g = heads / kv_heads;
+    const int qlen = seq_qlen[it.seq], pos0 = seq_pos0[it.seq];
+    const int slot = seq_slot[it.seq], tok0 = seq_qstart[it.seq];
+    const int rows_total = qlen * g;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const int r = it.row0 + warp;
+    const bool active = r < rows_total;
+    const int t = active ? r / g : 0;
+    const int hq = hk * g + (active ? r % g : 0);
+    const int pos = pos0 + t;
+    const float pen1 = r1[hq], pen2 = r2[hq];
+
+    pdl_wait();
+    for (int i = lane; i < dk; i += 32)
+        Qs[warp * dk + i] = active ? to_float(q[(size_t)(tok0 + t) * q_stride + hq * dk + i]) : 0.0f;
+
+    // the tile's key range: from the chunk of its first token to its last token
+    const int last_row = min(it.row0 + ROWS, rows_total) - 1;
+    const int max_pos = pos0 + last_row / g, min_pos = pos0 + it.row0 / g;
+    const int k_hi = min(it.kv_end, max_pos + 1);
+    int k_lo_true = it.kv_begin;
+    if (chunk > 0) k_lo_true = max(k_lo_true, min_pos / chunk * chunk);
+    const int k_lo = (k_lo_true / TILE) * TILE;
+    // this row's
+    int row_lo = it.kv_begin;
+    if (chunk > 0) row_lo = max(row_lo, pos / chunk * chunk);
+    const int row_hi = min(it.kv_end, pos + 1);
+
+    float m = -INFINITY, l = 0.0f;
+    float acc[MAX_D / 32];
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.0f;
+
+    for (int kt = k_lo; kt < k_hi; kt += TILE) {
+        __syncthreads();
+        for (int j = warp; j < TILE; j += ROWS) {        // a warp a key: whole rows of the pages
+            const int kpos = kt + j;
+            bool held = true, inside = kpos >= k_lo_true && kpos < k_hi;
+            size_t at = 0;
+            if (inside) {
+                const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
+                held = page_id >= 0 && page_id < num_pages;
+                at = ((size_t)page_id * kv_heads + hk) * page + (size_t)(kpos % page);
+            }
+            const bool read = inside && held;
+            for (int i = lane; i < dk; i += 32)
+                Ks[j * (dk + 1) + i] = read ? to_float(k_pages[at * dk + i]) : 0.0f;
+            for (int i = lane; i < dv; i += 32)
+                Vs[j * dv + i] = read ? to_float(v_pages[at * dv + i]) : 0.0f;
+            if (lane == 0) {
+                Ks[j * (dk + 1) + dk] = held ? 0.0f : -INFINITY;
+                if (!held && status != nullptr) atomicExch(status, 2);
+            }
+        }
+        __syncthreads();
+        if (!active) continue;
+
+        const int kpos = kt + lane;
+        const float* kr = Ks + lane * (dk + 1);
+        const bool valid = kpos >= row_lo && kpos < row_hi && kr[dk] == 0.0f;
+        const float* qr = Qs + warp * dk;
+        float s = 0.0f;
+        for (int i = 0; i < dk; ++i) s = fmaf(qr[i], kr[i], s);
+        s = valid ? s * scale - pen1 * log1pf(pen2 * (float)(pos - kpos)) : -INFINITY;
+        const float m_new = fmaxf(m, warp_max(s));
+        if (m_new == -INFINITY) continue;
+        const float p = valid ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m - m_new);
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < MAX_D / 32; ++i) acc[i] *= corr;
+        for (int j = 0; j < TILE; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            if (pj == 0.0f) continue;
+            const float* vr = Vs + j * dv;
+#pragma unroll
+            for (int i = 0; i < MAX_D / 32; ++i) {
+                const int dd = lane + 32 * i;
+                if (dd < dv) acc[i] = fmaf(pj, vr[dd], acc[i]);
+            }
+        }
+        m = m_new;
+    }
+    pdl_trigger();
+    if (!active) return;
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    T* o = out + (size_t)(tok0 + t) * out_stride + hq * dv;
+#pragma unroll
+    for (int i = 0; i < MAX_D / 32; ++i) {
+        const int dd = lane + 32 * i;
+        if (dd < dv) o[dd] = from_float<T>(acc[i] * inv);
+    }
+}
+
+}  // namespace
+
+DE_EXPORT int de_attn_chunk_rows() { return ROWS; }
+
+DE_EXPORT int de_kv_write_normed(int dtype, const void* proj, int ld, int k_col,
+                                 const int* positions, const int* token_slot, int G, int dk,
+                                 int dv, float eps, void* k_pages, void* v_pages,
+                                 const int* block_table, int table_stride, int page, int num_pages,
+                                 int n, int* status, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 64;
+    if (dtype == DE_BF16)
+        return de_launch(kv_write_normed_kernel<__nv_bfloat16>, dim3(n, G), dim3(threads), 0, s,
+                         (const __nv_bfloat16*)proj, ld, k_col, positions, token_slot, G, dk, dv,
+                         eps, (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
+                         table_stride, page, num_pages, status);
+    return de_launch(kv_write_normed_kernel<float>, dim3(n, G), dim3(threads), 0, s,
+                     (const float*)proj, ld, k_col, positions, token_slot, G, dk, dv, eps,
+                     (float*)k_pages, (float*)v_pages, block_table, table_stride, page, num_pages,
+                     status);
+}
+
+DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, int out_stride,
+                            const void* k_pages, const void* v_pages, const int* block_table,
+                            int table_stride, int num_pages, const int* seq_slot,
+                            const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
+                            const int* items, int num_items, const float* r1, const float* r2,
+                            int heads, int kv_heads, int dk, int dv, int page, float scale,
+                            int chunk, int* status, void* stream) {
+    if (num_items <= 0) return 0;
+    if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D || heads % kv_heads != 0) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)(TILE * (dk + 1) + TILE * dv + ROWS * dk) * sizeof(float);
+    dim3 grid(num_items, kv_heads);
+    cudaError_t e;
+#define LAUNCH(T)                                                                               \
+    do {                                                                                        \
+        if (smem > 48 * 1024) {                                                                 \
+            e = cudaFuncSetAttribute(attn_chunk_kernel<T>,                                      \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+            if (e != cudaSuccess) return (int)e;                                                \
+        }                                                                                       \
+        return de_launch(attn_chunk_kernel<T>, grid, dim3(ROWS * 32), smem, s, (const T*)q,     \
+                         q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages,   \
+                         block_table, table_stride, num_pages, seq_slot, seq_qstart, seq_qlen,  \
+                         seq_pos0, (const WorkItem*)items, r1, r2, heads, kv_heads, dk, dv, page, \
+                         scale, chunk, status);                                                 \
+    } while (0)
+    if (dtype == DE_BF16) LAUNCH(__nv_bfloat16);
+    LAUNCH(float);
+#undef LAUNCH
+}

@@ -205,6 +205,65 @@ DE_EXPORT int de_add_rmsnorm(int dtype, int weight_dtype, float* resid, const vo
 }
 
 // ------------------------------------------------------------------------------------------
+// The same norm in groups: the row is cut into `groups` equal consecutive parts and each part is
+// scaled by its own rsqrt(mean of its squares + eps); the weight spans the whole row.  A warp takes
+// a part at a time (parts are short: width / groups), so the order of a part's sum depends on the
+// part's length only.
+// ------------------------------------------------------------------------------------------
+template <typename T, typename W>
+__global__ void add_rmsnorm_grouped_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                           const W* __restrict__ weight, T* __restrict__ out,
+                                           const int* __restrict__ rows, int width, int groups,
+                                           float eps) {
+    const int i_out = blockIdx.x;
+    const int row = rows ? rows[i_out] : i_out;
+    float* r = resid + (size_t)row * width;
+    const T* d = delta ? delta + (size_t)row * width : nullptr;
+    const bool update = (rows == nullptr) && (delta != nullptr);
+    const int part = width / groups;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    pdl_wait();
+    T* o = out + (size_t)i_out * width;
+    for (int g = warp; g < groups; g += warps) {
+        const int base = g * part;
+        float ss = 0.0f;
+        for (int i = lane; i < part; i += 32) {
+            float x = r[base + i];
+            if (d) x += to_float(d[base + i]);
+            ss += x * x;
+        }
+        const float inv = rsqrtf(warp_sum(ss) / (float)part + eps);
+        for (int i = lane; i < part; i += 32) {
+            float x = r[base + i];
+            if (d) x += to_float(d[base + i]);       // the same sum as above, bit for bit
+            if (update) r[base + i] = x;
+            const float y = to_float(from_float<T>(x * inv));
+            o[base + i] = from_float<T>(y * to_float(weight[base + i]));
+        }
+    }
+    pdl_trigger();
+}
+
+DE_EXPORT int de_add_rmsnorm_grouped(int dtype, int weight_dtype, float* resid, const void* delta,
+                                     const void* weight, void* out, const int* rows, int n_out,
+                                     int width, int groups, float eps, void* stream) {
+    if (n_out <= 0) return 0;
+    if (groups <= 0 || width % groups != 0) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = groups >= 8 ? 256 : (groups >= 4 ? 128 : 32 * groups);
+#define GROUPED(T, W)                                                                          \
+    return de_launch(add_rmsnorm_grouped_kernel<T, W>, dim3(n_out), dim3(threads), 0, s, resid, \
+                     (const T*)delta, (const W*)weight, (T*)out, rows, width, groups, eps)
+    if (dtype == DE_BF16) {
+        if (weight_dtype == DE_BF16) GROUPED(__nv_bfloat16, __nv_bfloat16);
+        GROUPED(__nv_bfloat16, float);
+    }
+    if (weight_dtype == DE_BF16) GROUPED(float, __nv_bfloat16);
+    GROUPED(float, float);
+#undef GROUPED
+}
+
+// ------------------------------------------------------------------------------------------
 // rotation of q and k by position + write of k and v into the pages of the cache.
 //   qkv row = [q heads | k heads | v heads], each head `d` wide.
 //   pair (j, j + rot/2) of a head is rotated by angle = float(pos) * inv_freq[j]

@@ -1,0 +1,483 @@
+// Mixers that carry a matrix state per head from token to token: the gated delta rule with a
+// decay per key channel, and retention (a fixed decay per head, no softmax).  Both states live in
+// float32 in the slot of their request; everything here is float32 arithmetic, the storage type T
+// (float32 or bfloat16) is that of the projections that come in and of the rows that go out.
+//
+//   delta rule, per head, S [dk, dv]:   S <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);
+//                                       S <- S + k_t u^T;  o_t = S^T q_t
+//   retention, per head:                S <- decay S + k_t v_t^T;  o_t = S^T q_t
+//
+// The columns of S never meet: column j needs k_t, q_t, g_t, beta_t and v_t[j] only.  The scan
+// kernel therefore gives a column to four adjacent lanes (each holds a quarter of its rows in
+// registers), so a token costs two short chains of multiply-adds and two butterfly sums over four
+// lanes, and a block of 32 columns walks its sequence's tokens of the step one after the other
+// while the next tokens' vectors arrive through cp.async.  The order of every sum depends on the
+// head's sizes only: a state does not depend, bit for bit, on how its tokens were cut into steps.
+//
+// What is token-parallel runs before the scan in a kernel of its own: the short causal
+// convolution over time with its activation (its last taps - 1 inputs are part of the slot's
+// state), the unit norms of q and k, the gate beta and the decays for the delta rule; the rotation
+// by position for retention.  After the scan one more kernel normalises every head's output by its
+// root mean square and gates it.
+
+#include "common.cuh"
+
+DE_DEFINE_PDL_SWITCH
+
+namespace {
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
+
+// ------------------------------------------------------------------------------------------
+// Before the delta rule: one block a token.
+//   proj row = [q (G dk) | k (G dk) | v (H dv) | ...], b (H) from column b_col on: the stacked
+//   projection's output
+//   y[c] = silu(sum_j taps[c][j] * x[t - (K-1) + j][c]);  inputs before the step's first token of
+//   the sequence come from the slot's state, conv_state[i] = input at position pos0 - (K-1) + i
+//   (zeros at a sequence's start: the slot is zeroed at admission)
+//   q, k: each head divided by sqrt(sum of squares + 1e-6); q times dk^-1/2
+//   beta = sigmoid(b);  g = exp(-exp(A_log[h]) * softplus(a + dt_bias))
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void delta_prep_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ a,
+                                  const float* __restrict__ taps, const float* __restrict__ dt_bias,
+                                  const float* __restrict__ a_log, const float* __restrict__ state,
+                                  long long slot_stride, int conv_offset,
+                                  const int* __restrict__ token_seq,
+                                  const int* __restrict__ token_slot,
+                                  const int* __restrict__ positions,
+                                  const int* __restrict__ seq_pos0, float* __restrict__ qn,
+                                  float* __restrict__ kn, float* __restrict__ vv,
+                                  float* __restrict__ beta, float* __restrict__ gdec, int H, int G,
+                                  int dk, int dv, int K, int b_col) {
+    extern __shared__ float sh[];                    // [2 G dk]
+    const int n = blockIdx.x;
+    const int qk = 2 * G * dk, C = qk + H * dv;
+    const int seq = token_seq[n], slot = token_slot[n];
+    const int off = positions[n] - seq_pos0[seq];   // the token's place in its sequence's portion
+    pdl_wait();
+    const float* cs = state + (size_t)slot * slot_stride + conv_offset;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float acc = 0.0f;
+        for (int j = 0; j < K; ++j) {
+            const int rel = off - (K - 1) + j;
+            const float x = rel >= 0 ? to_float(proj[(size_t)(n - (K - 1) + j) * ld + c])
+                                     : cs[(size_t)(off + j) * C + c];
+            acc = fmaf(taps[c * K + j], x, acc);
+        }
+        const float y = silu_f(acc);
+        if (c < qk) sh[c] = y;
+        else vv[(size_t)n * (H * dv) + (c - qk)] = y;
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const float q_scale = 1.0f / sqrtf((float)dk);
+    for (int head = warp; head < 2 * G; head += warps) {
+        const float* x = sh + head * dk;
+        float ss = 0.0f;
+        for (int i = lane; i < dk; i += 32) ss = fmaf(x[i], x[i], ss);
+        const float inv = 1.0f / sqrtf(warp_sum(ss) + 1e-6f);
+        float* dst = head < G ? qn + (size_t)n * (G * dk) + head * dk
+                              : kn + (size_t)n * (G * dk) + (head - G) * dk;
+        for (int i = lane; i < dk; i += 32)
+            dst[i] = head < G ? (x[i] * inv) * q_scale : x[i] * inv;
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+        beta[(size_t)n * H + h] = sigmoid_f(to_float(proj[(size_t)n * ld + b_col + h]));
+    for (int i = threadIdx.x; i < H * dk; i += blockDim.x) {
+        const float rate = expf(a_log[i / dk]);
+        gdec[(size_t)n * (H * dk) + i] =
+            expf(-rate * softplus_f(a[(size_t)n * (H * dk) + i] + dt_bias[i]));
+    }
+    pdl_trigger();
+}
+
+// After a step: the slot keeps the last K - 1 inputs of the convolution.  One block a sequence.
+template <typename T>
+__global__ void conv_state_kernel(const T* __restrict__ proj, int ld, float* __restrict__ state,
+                                  long long slot_stride, int conv_offset,
+                                  const int* __restrict__ seq_slot,
+                                  const int* __restrict__ seq_qstart,
+                                  const int* __restrict__ seq_qlen, int C, int K) {
+    const int s = blockIdx.x;
+    const int qlen = seq_qlen[s], tok0 = seq_qstart[s];
+    pdl_wait();
+    pdl_trigger();
+    float* cs = state + (size_t)seq_slot[s] * slot_stride + conv_offset;
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+        for (int i = 0; i < K - 1; ++i) {            // ascending: what is read lies ahead
+            const int rel = qlen - (K - 1) + i;
+            cs[(size_t)i * C + c] = rel >= 0 ? to_float(proj[(size_t)(tok0 + rel) * ld + c])
+                                             : cs[(size_t)(i + qlen) * C + c];
+        }
+}
+
+// ------------------------------------------------------------------------------------------
+// Before retention: q and k rotated by position (pairs (i, i + rot/2) of the first `rot` features
+// of a head, angle = float(position) * inv_freq[i], the rest unchanged), k times dk^-1/2 after.
+//   proj row = [q (H dk) | k (H dk) | v | gate]; out: qr, kr float32 [N, H dk]
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void retention_prep_kernel(const T* __restrict__ proj, int ld,
+                                      const int* __restrict__ positions,
+                                      const float* __restrict__ inv_freq, int rot, int H, int dk,
+                                      float* __restrict__ qr, float* __restrict__ kr) {
+    const int n = blockIdx.x;
+    const float pos = (float)positions[n];
+    const int half = rot / 2, per = dk - half;      // work items a head: pairs, then plain features
+    const float k_scale = 1.0f / sqrtf((float)dk);
+    pdl_wait();
+    for (int idx = threadIdx.x; idx < 2 * H * per; idx += blockDim.x) {
+        const int which = idx / (H * per), rest = idx - which * (H * per);
+        const int h = rest / per, i = rest - h * per;
+        const T* src = proj + (size_t)n * ld + which * (H * dk) + h * dk;
+        float* dst = (which ? kr : qr) + (size_t)n * (H * dk) + h * dk;
+        const float scale = which ? k_scale : 1.0f;
+        if (i < half) {
+            float s, c;
+            sincosf(pos * inv_freq[i], &s, &c);
+            float ra, rb;
+            rope_rotate(to_float(src[i]), to_float(src[i + half]), c, s, ra, rb);
+            dst[i] = ra * scale;
+            dst[i + half] = rb * scale;
+        } else {
+            dst[i + half] = to_float(src[i + half]) * scale;
+        }
+    }
+    pdl_trigger();
+}
+
+// ------------------------------------------------------------------------------------------
+// The scan.  grid (sequences, heads, column blocks of COLS); thread = 4 * column + quarter.
+// Row i of the state belongs to quarter i % 4, register i / 4; in shared memory a token's vector
+// lies quarter by quarter (quarter l at l * (R + 4)), so a quarter reads its share as float4 and
+// the four quarters of a warp hit different banks.
+// ------------------------------------------------------------------------------------------
+constexpr int COLS = 32;
+constexpr int TB = 8;          // tokens whose vectors are in flight together
+
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+template <typename VT, int R, bool DELTA>
+__global__ void __launch_bounds__(COLS * 4)
+scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
+            const VT* __restrict__ v, int ldv, const float* __restrict__ g, int ldg,
+            const float* __restrict__ beta, int ldb, const float* __restrict__ decay,
+            float* __restrict__ state, long long slot_stride, float* __restrict__ out,
+            const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
+            const int* __restrict__ seq_qlen, int H, int rep, int dk, int dv) {
+    constexpr int PD = 4 * (R + 4);                  // a token's vector in shared memory
+    constexpr int VECS = DELTA ? 3 : 2;              // q, k (, g)
+    extern __shared__ __align__(16) float buf[];     // [2][TB][VECS][PD]
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int col = blockIdx.z * COLS + (threadIdx.x >> 2), l = threadIdx.x & 3;
+    const bool live = col < dv;
+    const int qlen = seq_qlen[s], tok0 = seq_qstart[s];
+    const int hk = h / rep;                          // the q/k head this head reads
+    for (int i = threadIdx.x; i < 2 * TB * VECS * PD; i += COLS * 4) buf[i] = 0.0f;
+    __syncthreads();                                 // the padding stays zero from here on
+    pdl_wait();
+
+    float* S_g = state + (size_t)seq_slot[s] * slot_stride + (size_t)h * dk * dv;
+    float S[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = 4 * r + l;
+        S[r] = (live && i < dk) ? S_g[(size_t)i * dv + col] : 0.0f;
+    }
+    const float dec = DELTA ? 0.0f : decay[h];
+
+    auto issue = [&](int b) {
+        float* dst = buf + (size_t)(b & 1) * TB * VECS * PD;
+        const int count = min(TB, qlen - b * TB);
+        for (int idx = threadIdx.x; idx < count * dk; idx += COLS * 4) {
+            const int t = idx / dk, i = idx - t * dk;
+            const size_t tok = (size_t)(tok0 + b * TB + t);
+            float* d = dst + (size_t)t * VECS * PD + (i & 3) * (R + 4) + (i >> 2);
+            cp_async4(d, q + tok * ldq + hk * dk + i);
+            cp_async4(d + PD, k + tok * ldk + hk * dk + i);
+            if (DELTA) cp_async4(d + 2 * PD, g + tok * ldg + h * dk + i);
+        }
+        cp_async_commit();
+    };
+
+    const int batches = (qlen + TB - 1) / TB;
+    if (batches > 0) issue(0);
+    for (int b = 0; b < batches; ++b) {
+        const int count = min(TB, qlen - b * TB);
+        // this batch's values and gates: loads that do not depend on the state, asked for early
+        float vt[TB], bt[TB];
+#pragma unroll
+        for (int t = 0; t < TB; ++t) {
+            const size_t tok = (size_t)(tok0 + b * TB + t);
+            vt[t] = (live && t < count) ? to_float(v[tok * ldv + h * dv + col]) : 0.0f;
+            bt[t] = (DELTA && t < count) ? beta[tok * ldb + h] : 0.0f;
+        }
+        if (b + 1 < batches) {
+            issue(b + 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const float* src = buf + (size_t)(b & 1) * TB * VECS * PD + l * (R + 4);
+#pragma unroll
+        for (int t = 0; t < TB; ++t) {
+            if (t >= count) break;
+            const float4* q4 = reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD);
+            const float4* k4 = reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD + PD);
+            float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+            if (DELTA) {
+                const float4* g4 =
+                    reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD + 2 * PD);
+                float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+#pragma unroll
+                for (int r = 0; r < R / 4; ++r) {
+                    const float4 gg = g4[r], kk = k4[r];
+                    S[4 * r + 0] *= gg.x; p0 = fmaf(S[4 * r + 0], kk.x, p0);
+                    S[4 * r + 1] *= gg.y; p1 = fmaf(S[4 * r + 1], kk.y, p1);
+                    S[4 * r + 2] *= gg.z; p2 = fmaf(S[4 * r + 2], kk.z, p2);
+                    S[4 * r + 3] *= gg.w; p3 = fmaf(S[4 * r + 3], kk.w, p3);
+                }
+                float part = (p0 + p1) + (p2 + p3);
+                part += __shfl_xor_sync(0xffffffffu, part, 1);
+                part += __shfl_xor_sync(0xffffffffu, part, 2);
+                const float u = bt[t] * (vt[t] - part);
+#pragma unroll
+                for (int r = 0; r < R / 4; ++r) {
+                    const float4 kk = k4[r], qq = q4[r];
+                    S[4 * r + 0] = fmaf(kk.x, u, S[4 * r + 0]); o0 = fmaf(S[4 * r + 0], qq.x, o0);
+                    S[4 * r + 1] = fmaf(kk.y, u, S[4 * r + 1]); o1 = fmaf(S[4 * r + 1], qq.y, o1);
+                    S[4 * r + 2] = fmaf(kk.z, u, S[4 * r + 2]); o2 = fmaf(S[4 * r + 2], qq.z, o2);
+                    S[4 * r + 3] = fmaf(kk.w, u, S[4 * r + 3]); o3 = fmaf(S[4 * r + 3], qq.w, o3);
+                }
+            } else {
+                const float u = vt[t];
+#pragma unroll
+                for (int r = 0; r < R / 4; ++r) {
+                    const float4 kk = k4[r], qq = q4[r];
+                    S[4 * r + 0] = fmaf(kk.x, u, S[4 * r + 0] * dec); o0 = fmaf(S[4 * r + 0], qq.x, o0);
+                    S[4 * r + 1] = fmaf(kk.y, u, S[4 * r + 1] * dec); o1 = fmaf(S[4 * r + 1], qq.y, o1);
+                    S[4 * r + 2] = fmaf(kk.z, u, S[4 * r + 2] * dec); o2 = fmaf(S[4 * r + 2], qq.z, o2);
+                    S[4 * r + 3] = fmaf(kk.w, u, S[4 * r + 3] * dec); o3 = fmaf(S[4 * r + 3], qq.w, o3);
+                }
+            }
+            float o = (o0 + o1) + (o2 + o3);
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (live && l == 0)
+                out[(size_t)(tok0 + b * TB + t) * (H * dv) + h * dv + col] = o;
+        }
+        __syncthreads();                             // the buffer may be filled again
+    }
+    pdl_trigger();
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int i = 4 * r + l;
+            if (i < dk) S_g[(size_t)i * dv + col] = S[r];
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// After the scan: every head's output over its root mean square, gated.  A warp a (token, head).
+//   mode 0: out = o / rms * weight[j] * sigmoid(gate)   gate float32 [N, H dv]
+//   mode 1: out = o / rms * silu(gate)                  gate of type T, row stride ld_gate
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void head_gate_kernel(const float* __restrict__ o, const void* __restrict__ gate,
+                                 int ld_gate, const float* __restrict__ weight,
+                                 T* __restrict__ out, int n_tokens, int H, int dv, float eps,
+                                 int mode) {
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    pdl_wait();
+    pdl_trigger();
+    if (item >= n_tokens * H) return;
+    const int n = item / H, h = item - n * H;
+    const float* x = o + (size_t)n * (H * dv) + h * dv;
+    float ss = 0.0f;
+    for (int j = lane; j < dv; j += 32) ss = fmaf(x[j], x[j], ss);
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+    T* dst = out + (size_t)n * (H * dv) + h * dv;
+    for (int j = lane; j < dv; j += 32) {
+        float y = x[j] * inv;
+        if (mode == 0) {
+            const float gt = ((const float*)gate)[(size_t)n * ld_gate + h * dv + j];
+            y = y * weight[j] * sigmoid_f(gt);
+        } else {
+            const float gt = to_float(((const T*)gate)[(size_t)n * ld_gate + h * dv + j]);
+            y = y * silu_f(gt);
+        }
+        dst[j] = from_float<T>(y);
+    }
+}
+
+// out = (a / rms(a) * wa + b / rms(b) * wb) / 2 over the model width.  One block a token.
+template <typename T>
+__global__ void mean_of_normed_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                      const float* __restrict__ wa, const float* __restrict__ wb,
+                                      T* __restrict__ out, int width, float eps) {
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * width;
+    pdl_wait();
+    float sa = 0.0f, sb = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float x = to_float(a[base + i]), y = to_float(b[base + i]);
+        sa = fmaf(x, x, sa);
+        sb = fmaf(y, y, sb);
+    }
+    const float ia = 1.0f / sqrtf(block_sum(sa, scratch) / (float)width + eps);
+    const float ib = 1.0f / sqrtf(block_sum(sb, scratch) / (float)width + eps);
+    pdl_trigger();
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float x = to_float(a[base + i]) * ia * wa[i];
+        const float y = to_float(b[base + i]) * ib * wb[i];
+        out[base + i] = from_float<T>(0.5f * (x + y));
+    }
+}
+
+template <typename VT, bool DELTA>
+int launch_scan(int R, dim3 grid, cudaStream_t s, const float* q, int ldq, const float* k, int ldk,
+                const VT* v, int ldv, const float* g, int ldg, const float* beta, int ldb,
+                const float* decay, float* state, long long slot_stride, float* out,
+                const int* seq_slot, const int* seq_qstart, const int* seq_qlen, int H, int rep,
+                int dk, int dv) {
+#define SCAN(RR)                                                                                \
+    do {                                                                                        \
+        const size_t smem = (size_t)2 * TB * (DELTA ? 3 : 2) * 4 * (RR + 4) * sizeof(float);    \
+        if (smem > 48 * 1024) {                                                                 \
+            cudaError_t e = cudaFuncSetAttribute(scan_kernel<VT, RR, DELTA>,                    \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                                 (int)smem);                                    \
+            if (e != cudaSuccess) return (int)e;                                                \
+        }                                                                                       \
+        return de_launch(scan_kernel<VT, RR, DELTA>, grid, dim3(COLS * 4), smem, s, q, ldq, k,  \
+                         ldk, v, ldv, g, ldg, beta, ldb, decay, state, slot_stride, out,        \
+                         seq_slot, seq_qstart, seq_qlen, H, rep, dk, dv);                       \
+    } while (0)
+    if (R <= 8) SCAN(8);
+    if (R <= 16) SCAN(16);
+    if (R <= 32) SCAN(32);
+    SCAN(64);
+#undef SCAN
+}
+
+}  // namespace
+
+DE_EXPORT int de_recurrent_max_key_dim() { return 256; }
+
+DE_EXPORT int de_delta_prep(int dtype, const void* proj, int ld, const float* a, const float* taps,
+                            const float* dt_bias, const float* a_log, const float* state,
+                            long long slot_stride, int conv_offset, const int* token_seq,
+                            const int* token_slot, const int* positions, const int* seq_pos0,
+                            float* qn, float* kn, float* vv, float* beta, float* gdec, int n, int H,
+                            int G, int dk, int dv, int K, int b_col, void* stream) {
+    if (n <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || K <= 0) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem = (size_t)2 * G * dk * sizeof(float);
+    if (smem > 48 * 1024) return -3;
+#define PREP(T)                                                                                 \
+    return de_launch(delta_prep_kernel<T>, dim3(n), dim3(256), smem, s, (const T*)proj, ld, a,  \
+                     taps, dt_bias, a_log, state, slot_stride, conv_offset, token_seq,          \
+                     token_slot, positions, seq_pos0, qn, kn, vv, beta, gdec, H, G, dk, dv, K,  \
+                     b_col)
+    if (dtype == DE_BF16) PREP(__nv_bfloat16);
+    PREP(float);
+#undef PREP
+}
+
+DE_EXPORT int de_conv_state(int dtype, const void* proj, int ld, float* state,
+                            long long slot_stride, int conv_offset, const int* seq_slot,
+                            const int* seq_qstart, const int* seq_qlen, int n_seqs, int C, int K,
+                            void* stream) {
+    if (n_seqs <= 0 || K <= 1) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        return de_launch(conv_state_kernel<__nv_bfloat16>, dim3(n_seqs), dim3(256), 0, s,
+                         (const __nv_bfloat16*)proj, ld, state, slot_stride, conv_offset, seq_slot,
+                         seq_qstart, seq_qlen, C, K);
+    return de_launch(conv_state_kernel<float>, dim3(n_seqs), dim3(256), 0, s, (const float*)proj,
+                     ld, state, slot_stride, conv_offset, seq_slot, seq_qstart, seq_qlen, C, K);
+}
+
+DE_EXPORT int de_retention_prep(int dtype, const void* proj, int ld, const int* positions,
+                                const float* inv_freq, int rot, int H, int dk, float* qr, float* kr,
+                                int n, void* stream) {
+    if (n <= 0) return 0;
+    if (rot < 0 || rot % 2 || rot > dk) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        return de_launch(retention_prep_kernel<__nv_bfloat16>, dim3(n), dim3(256), 0, s,
+                         (const __nv_bfloat16*)proj, ld, positions, inv_freq, rot, H, dk, qr, kr);
+    return de_launch(retention_prep_kernel<float>, dim3(n), dim3(256), 0, s, (const float*)proj,
+                     ld, positions, inv_freq, rot, H, dk, qr, kr);
+}
+
+// v_dtype: the type of v (DE_F32 for the delta rule, whose values come from its own preparation).
+// delta 1: g [N, ldg] and beta [N, ldb] are used; 0: decay [H].
+DE_EXPORT int de_state_scan(int delta, int v_dtype, const float* q, int ldq, const float* k,
+                            int ldk, const void* v, int ldv, const float* g, int ldg,
+                            const float* beta, int ldb, const float* decay, float* state,
+                            long long slot_stride, float* out, const int* seq_slot,
+                            const int* seq_qstart, const int* seq_qlen, int n_seqs, int H, int rep,
+                            int dk, int dv, void* stream) {
+    if (n_seqs <= 0) return 0;
+    if (dk <= 0 || dk > 256 || dv <= 0 || H <= 0 || rep <= 0 || H % rep) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int R = (dk + 3) / 4;
+    dim3 grid(n_seqs, H, (dv + COLS - 1) / COLS);
+    if (delta) {
+        if (v_dtype != DE_F32) return -4;
+        return launch_scan<float, true>(R, grid, s, q, ldq, k, ldk, (const float*)v, ldv, g, ldg,
+                                        beta, ldb, decay, state, slot_stride, out, seq_slot,
+                                        seq_qstart, seq_qlen, H, rep, dk, dv);
+    }
+    if (v_dtype == DE_BF16)
+        return launch_scan<__nv_bfloat16, false>(R, grid, s, q, ldq, k, ldk,
+                                                 (const __nv_bfloat16*)v, ldv, g, ldg, beta, ldb,
+                                                 decay, state, slot_stride, out, seq_slot,
+                                                 seq_qstart, seq_qlen, H, rep, dk, dv);
+    return launch_scan<float, false>(R, grid, s, q, ldq, k, ldk, (const float*)v, ldv, g, ldg,
+                                     beta, ldb, decay, state, slot_stride, out, seq_slot,
+                                     seq_qstart, seq_qlen, H, rep, dk, dv);
+}
+
+DE_EXPORT int de_head_gate(int dtype, const float* o, const void* gate, int ld_gate,
+                           const float* weight, void* out, int n, int H, int dv, float eps,
+                           int mode, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int warps = 4;
+    dim3 grid((n * H + warps - 1) / warps);
+    if (dtype == DE_BF16)
+        return de_launch(head_gate_kernel<__nv_bfloat16>, grid, dim3(warps * 32), 0, s, o, gate,
+                         ld_gate, weight, (__nv_bfloat16*)out, n, H, dv, eps, mode);
+    return de_launch(head_gate_kernel<float>, grid, dim3(warps * 32), 0, s, o, gate, ld_gate,
+                     weight, (float*)out, n, H, dv, eps, mode);
+}
+
+DE_EXPORT int de_mean_of_normed(int dtype, const void* a, const void* b, const float* wa,
+                                const float* wb, void* out, int n, int width, float eps,
+                                void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (dtype == DE_BF16)
+        return de_launch(mean_of_normed_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s,
+                         (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, wa, wb,
+                         (__nv_bfloat16*)out, width, eps);
+    return de_launch(mean_of_normed_kernel<float>, dim3(n), dim3(threads), 0, s, (const float*)a,
+                     (const float*)b, wa, wb, (float*)out, width, eps);
+}

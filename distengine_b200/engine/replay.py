@@ -32,7 +32,7 @@ from ..config.engine import parse_dtype
 from ..models.loading import load_model
 from .step import StepEntry, StepRunner
 
-LIVE_REQUESTS = 8          # slots; a trace holds up to four live requests
+LIVE_REQUESTS = 4          # slots: a trace holds up to four live requests, so slots are used again
 
 
 def build_runner(model_dir: str, dtype: "str | torch.dtype", max_tokens: int,

@@ -38,6 +38,8 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "attention_decode": ("attention_decode.cu", ()),    # built per head size: HEAD_DIM=<d>
     "linear_mid": ("linear_mid.cu", ("cuda",)),
     "attention_tcgen05": ("attention_tcgen05.cu", ()),  # built per head size: HEAD_DIM=64|128
+    "attention_chunk": ("attention_chunk.cu", ()),
+    "recurrent": ("recurrent.cu", ()),
 }
 
 

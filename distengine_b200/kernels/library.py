@@ -17,7 +17,7 @@ class KernelsUnavailable(RuntimeError):
     pass
 
 
-P, I, F = c_void_p, c_int, c_float
+P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
 
 # module -> {function: argument types}; every function returns an int (0, or a CUDA error code,
 # or a negative number for arguments the kernel refuses)
@@ -25,6 +25,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
     "core": {
         "de_embed_rows": [I, P, P, P, I, I, I, P],
         "de_add_rmsnorm": [I, I, P, P, P, P, P, I, I, F, P],
+        "de_add_rmsnorm_grouped": [I, I, P, P, P, P, P, I, I, I, F, P],
         "de_rope_kv_write": [I, P, I, P, P, P, I, I, I, I, P, P, P, I, I, I, I, I, P, P],
         "de_silu_mul": [I, P, P, I, I, P],
         "de_sample_rows": [P, I, I, P, P, P, P, P],
@@ -60,6 +61,23 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_attn_mma_head_dim": [], "de_attn_mma_rows": [I],
         "de_attn_mma": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, F, I, P,
                         P],
+    },
+    "attention_chunk": {
+        "de_attn_chunk_rows": [],
+        "de_kv_write_normed": [I, P, I, I, P, P, I, I, I, F, P, P, P, I, I, I, I, P, P],
+        "de_attn_chunk": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, I, F,
+                          I, P, P],
+    },
+    "recurrent": {
+        "de_recurrent_max_key_dim": [],
+        "de_delta_prep": [I, P, I, P, P, P, P, P, L, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I,
+                          I, I, P],
+        "de_conv_state": [I, P, I, P, L, I, P, P, P, I, I, I, P],
+        "de_retention_prep": [I, P, I, P, P, I, I, I, P, P, I, P],
+        "de_state_scan": [I, I, P, I, P, I, P, I, P, I, P, I, P, P, L, P, P, P, P, I, I, I, I, I,
+                          P],
+        "de_head_gate": [I, P, P, I, P, P, I, I, I, F, I, P],
+        "de_mean_of_normed": [I, P, P, P, P, P, I, I, F, P],
     },
     "attention_decode": {
         "de_attn_decode_head_dim": [], "de_attn_decode_max_cluster": [],

@@ -88,9 +88,11 @@ def embed_rows(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> Non
 
 # ------------------------------------------------------------------------------- norm
 def add_rmsnorm(resid: torch.Tensor, delta: "torch.Tensor | None", weight: torch.Tensor,
-                eps: float, out: torch.Tensor, rows: "torch.Tensor | None" = None) -> None:
+                eps: float, out: torch.Tensor, rows: "torch.Tensor | None" = None,
+                groups: int = 1) -> None:
     """out = rmsnorm(resid + delta) * weight; resid (float32) takes the sum unless ``rows`` picks
-    the rows to normalise (then out[i] comes from row rows[i] and resid is not written)."""
+    the rows to normalise (then out[i] comes from row rows[i] and resid is not written).
+    ``groups`` > 1: every one of that many equal parts of a row has its own root mean square."""
     width = resid.shape[1]
     n_out = resid.shape[0] if rows is None else rows.shape[0]
     _need(resid.dtype == torch.float32 and resid.is_contiguous(), "resid must be float32")
@@ -103,6 +105,13 @@ def add_rmsnorm(resid: torch.Tensor, delta: "torch.Tensor | None", weight: torch
     if rows is not None:
         _i32(rows, "rows")
     lib = library.load("core")
+    if groups != 1:
+        _need(groups > 0 and width % groups == 0, "add_rmsnorm: groups must divide the width")
+        _check(lib.de_add_rmsnorm_grouped(_tag(out.dtype), _tag(weight.dtype), resid.data_ptr(),
+                                          _ptr(delta), weight.data_ptr(), out.data_ptr(),
+                                          _ptr(rows), n_out, width, groups, float(eps),
+                                          _stream()), "add_rmsnorm (grouped)")
+        return
     _check(lib.de_add_rmsnorm(_tag(out.dtype), _tag(weight.dtype), resid.data_ptr(), _ptr(delta),
                               weight.data_ptr(), out.data_ptr(), _ptr(rows), n_out, width,
                               float(eps), _stream()), "add_rmsnorm")

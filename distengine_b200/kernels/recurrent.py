@@ -1,0 +1,212 @@
+"""The kernels of the mixers that carry a state from token to token (``csrc/recurrent.cu``) and of
+the chunk-masked attention (``csrc/attention_chunk.cu``) as functions of torch tensors.  Like
+``ops``: every function launches on the current stream and checks what it passes on.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import library
+from .ops import _check, _i32, _need, _ptr, _stream, _tag
+
+
+def _f32(t: torch.Tensor, name: str) -> None:
+    _need(t.dtype == torch.float32 and t.is_cuda and t.stride(-1) == 1,
+          f"{name} must be a float32 CUDA tensor with contiguous rows")
+
+
+def max_key_dim() -> int:
+    return 256
+
+
+def delta_prep(proj: torch.Tensor, a: torch.Tensor, taps: torch.Tensor, dt_bias: torch.Tensor,
+               a_log: torch.Tensor, state: torch.Tensor, conv_offset: int, ctx, qn: torch.Tensor,
+               kn: torch.Tensor, vv: torch.Tensor, beta: torch.Tensor, gdec: torch.Tensor,
+               heads: int, kv_heads: int, key_dim: int, value_dim: int, b_col: int) -> None:
+    """What the delta rule needs of every token, from the stacked projection ``proj``
+    = [q (G dk) | k (G dk) | v (H dv) | ...] with b (H) from column ``b_col`` on, and ``a`` float32 [N, H dk] (the low-rank
+    decay projection): convolution over time with silu (its earlier inputs from ``state``
+    [slots, n] at ``conv_offset``), unit q and k (float32 [N, G dk]; q also times dk^-1/2), values
+    float32 [N, H dv], beta float32 [N, H], decays float32 [N, H dk]."""
+    n, taps_k = proj.shape[0], taps.shape[1]
+    qk, c = 2 * kv_heads * key_dim, 2 * kv_heads * key_dim + heads * value_dim
+    _need(proj.stride(1) == 1 and b_col >= c and proj.shape[1] >= b_col + heads,
+          "delta_prep: proj is too narrow")
+    for t, name, shape in ((a, "a", (n, heads * key_dim)), (taps, "taps", (c, taps_k)),
+                           (dt_bias, "dt_bias", (heads * key_dim,)), (a_log, "a_log", (heads,)),
+                           (qn, "qn", (n, qk // 2)), (kn, "kn", (n, qk // 2)),
+                           (vv, "vv", (n, heads * value_dim)), (beta, "beta", (n, heads)),
+                           (gdec, "gdec", (n, heads * key_dim))):
+        _f32(t, name)
+        _need(tuple(t.shape) == shape and t.is_contiguous(), f"delta_prep: {name} must be "
+              f"contiguous {list(shape)}")
+    _f32(state, "state")
+    _need(state.dim() == 2 and conv_offset + (taps_k - 1) * c <= state.shape[1],
+          "delta_prep: the state rows are too short for the convolution's inputs")
+    lib = library.load("recurrent")
+    _check(lib.de_delta_prep(_tag(proj.dtype), proj.data_ptr(), proj.stride(0), a.data_ptr(),
+                             taps.data_ptr(), dt_bias.data_ptr(), a_log.data_ptr(),
+                             state.data_ptr(), state.stride(0), conv_offset,
+                             ctx.token_seq.data_ptr(), ctx.token_slot.data_ptr(),
+                             ctx.positions.data_ptr(), ctx.seq_pos0.data_ptr(), qn.data_ptr(),
+                             kn.data_ptr(), vv.data_ptr(), beta.data_ptr(), gdec.data_ptr(), n,
+                             heads, kv_heads, key_dim, value_dim, taps_k, b_col, _stream()),
+           "delta_prep")
+
+
+def conv_state(proj: torch.Tensor, state: torch.Tensor, conv_offset: int, channels: int,
+               taps: int, ctx) -> None:
+    """The slots keep the last ``taps - 1`` inputs of the convolution (the first ``channels``
+    columns of ``proj``) of every sequence of the step."""
+    _f32(state, "state")
+    lib = library.load("recurrent")
+    _check(lib.de_conv_state(_tag(proj.dtype), proj.data_ptr(), proj.stride(0), state.data_ptr(),
+                             state.stride(0), conv_offset, ctx.seq_slot.data_ptr(),
+                             ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs,
+                             channels, taps, _stream()), "conv_state")
+
+
+def retention_prep(proj: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, heads: int,
+                   key_dim: int, qr: torch.Tensor, kr: torch.Tensor, ctx) -> None:
+    """q and k ([q (H dk) | k (H dk) | ...] in ``proj``) rotated by position into float32
+    [N, H dk]; k also times dk^-1/2."""
+    n = proj.shape[0]
+    _need(proj.stride(1) == 1 and proj.shape[1] >= 2 * heads * key_dim,
+          "retention_prep: proj is too narrow")
+    _f32(inv_freq, "inv_freq")
+    _need(inv_freq.shape == (rotary_dim // 2,) and rotary_dim % 2 == 0 and rotary_dim <= key_dim,
+          "retention_prep: inv_freq must be [rotary_dim / 2], rotary_dim even and <= key_dim")
+    for t in (qr, kr):
+        _f32(t, "rotated rows")
+        _need(tuple(t.shape) == (n, heads * key_dim) and t.is_contiguous(),
+              "retention_prep: outputs must be contiguous [N, H dk]")
+    lib = library.load("recurrent")
+    _check(lib.de_retention_prep(_tag(proj.dtype), proj.data_ptr(), proj.stride(0),
+                                 ctx.positions.data_ptr(), inv_freq.data_ptr(), rotary_dim, heads,
+                                 key_dim, qr.data_ptr(), kr.data_ptr(), n, _stream()),
+           "retention_prep")
+
+
+def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor,
+               out: torch.Tensor, heads: int, qk_heads: int, key_dim: int, value_dim: int, ctx,
+               g: "torch.Tensor | None" = None, beta: "torch.Tensor | None" = None,
+               decay: "torch.Tensor | None" = None) -> None:
+    """Walk every sequence's tokens of the step through its state ``state`` [slots, >= H dk dv]
+    (float32, rows [h][key channel][value channel] at the front) and write the read-outs, float32
+    [N, H dv].  With ``g`` [N, H dk] and ``beta`` [N, H]: the delta rule with a decay per key
+    channel.  With ``decay`` [H]: retention.  q, k float32 [N, qk_heads dk]; v [N, H dv] in
+    float32 or the activation dtype (any row stride)."""
+    n = q.shape[0]
+    delta = g is not None
+    _need(delta != (decay is not None) and (beta is not None) == delta,
+          "state_scan: give g and beta, or decay")
+    _need(key_dim <= max_key_dim(), f"state_scan: key size {key_dim} is beyond {max_key_dim()}")
+    for t, name in ((q, "q"), (k, "k"), (state, "state"), (out, "out")):
+        _f32(t, name)
+    _need(q.shape == k.shape == (n, qk_heads * key_dim) and heads % qk_heads == 0,
+          "state_scan: q and k must be [N, qk_heads dk]")
+    _need(v.stride(1) == 1 and v.shape == (n, heads * value_dim), "state_scan: v [N, H dv]")
+    _need(out.is_contiguous() and tuple(out.shape) == (n, heads * value_dim),
+          "state_scan: out must be contiguous [N, H dv]")
+    _need(state.dim() == 2 and state.shape[1] >= heads * key_dim * value_dim,
+          "state_scan: the state rows are too short")
+    if delta:
+        _f32(g, "g"), _f32(beta, "beta")
+        _need(g.shape == (n, heads * key_dim) and beta.shape == (n, heads)
+              and v.dtype == torch.float32, "state_scan: g [N, H dk], beta [N, H], v float32")
+    else:
+        _f32(decay, "decay")
+        _need(decay.shape == (heads,) and decay.is_contiguous(), "state_scan: decay [H]")
+    lib = library.load("recurrent")
+    _check(lib.de_state_scan(int(delta), _tag(v.dtype), q.data_ptr(), q.stride(0), k.data_ptr(),
+                             k.stride(0), v.data_ptr(), v.stride(0), _ptr(g),
+                             g.stride(0) if delta else 0, _ptr(beta),
+                             beta.stride(0) if delta else 0, _ptr(decay), state.data_ptr(),
+                             state.stride(0), out.data_ptr(), ctx.seq_slot.data_ptr(),
+                             ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, heads,
+                             heads // qk_heads, key_dim, value_dim, _stream()), "state_scan")
+
+
+def head_gate(o: torch.Tensor, gate: torch.Tensor, weight: "torch.Tensor | None",
+              out: torch.Tensor, heads: int, value_dim: int, eps: float) -> None:
+    """out = o / rms(o over each head) * weight * sigmoid(gate) with a float32 ``gate`` and a
+    ``weight`` [dv]; or, without a weight, o / rms * silu(gate) with a gate of out's dtype."""
+    n = o.shape[0]
+    _f32(o, "o")
+    _need(o.is_contiguous() and o.shape == (n, heads * value_dim) and out.is_contiguous()
+          and out.shape == o.shape and gate.stride(1) == 1 and gate.shape == o.shape,
+          "head_gate: o, gate and out must be [N, H dv]")
+    if weight is not None:
+        _f32(weight, "weight"), _f32(gate, "gate")
+        _need(weight.shape == (value_dim,), "head_gate: weight [dv]")
+    else:
+        _need(gate.dtype == out.dtype, "head_gate: a silu gate has the output's dtype")
+    lib = library.load("recurrent")
+    _check(lib.de_head_gate(_tag(out.dtype), o.data_ptr(), gate.data_ptr(), gate.stride(0),
+                            _ptr(weight), out.data_ptr(), n, heads, value_dim, float(eps),
+                            0 if weight is not None else 1, _stream()), "head_gate")
+
+
+def mean_of_normed(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor,
+                   out: torch.Tensor, eps: float) -> None:
+    """out = (a / rms(a) * wa + b / rms(b) * wb) / 2, rows over the width, float32 arithmetic."""
+    n, width = a.shape
+    _need(a.is_contiguous() and b.is_contiguous() and out.is_contiguous()
+          and a.shape == b.shape == out.shape and a.dtype == b.dtype == out.dtype,
+          "mean_of_normed: a, b and out must be contiguous, of one shape and dtype")
+    _f32(wa, "wa"), _f32(wb, "wb")
+    _need(wa.shape == wb.shape == (width,), "mean_of_normed: weights [width]")
+    lib = library.load("recurrent")
+    _check(lib.de_mean_of_normed(_tag(out.dtype), a.data_ptr(), b.data_ptr(), wa.data_ptr(),
+                                 wb.data_ptr(), out.data_ptr(), n, width, float(eps), _stream()),
+           "mean_of_normed")
+
+
+# ------------------------------------------------------------------------------- chunk attention
+def chunk_rows_per_tile() -> int:
+    return int(library.load("attention_chunk").de_attn_chunk_rows())
+
+
+def kv_write_normed(proj: torch.Tensor, k_col: int, kv_heads: int, key_dim: int, value_dim: int,
+                    eps: float, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                    block_table: torch.Tensor, ctx) -> None:
+    """Store every token's keys ([k (G dk) | v (G dv)] from column ``k_col`` of ``proj``) and its
+    values, each head's divided by its root mean square, in the pages."""
+    _need(proj.stride(1) == 1 and proj.shape[1] >= k_col + kv_heads * (key_dim + value_dim)
+          and proj.dtype == k_pages.dtype == v_pages.dtype, "kv_write_normed: proj and pages")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+          and tuple(k_pages.shape[1:]) == (kv_heads, k_pages.shape[2], key_dim)
+          and tuple(v_pages.shape) == (*k_pages.shape[:3], value_dim),
+          "kv_write_normed: pages must be [pages, kv_heads, page, dk] and [..., dv]")
+    _i32(block_table, "block_table")
+    lib = library.load("attention_chunk")
+    _check(lib.de_kv_write_normed(_tag(proj.dtype), proj.data_ptr(), proj.stride(0), k_col,
+                                  ctx.positions.data_ptr(), ctx.token_slot.data_ptr(), kv_heads,
+                                  key_dim, value_dim, float(eps), k_pages.data_ptr(),
+                                  v_pages.data_ptr(), block_table.data_ptr(),
+                                  block_table.stride(0), k_pages.shape[2], k_pages.shape[0],
+                                  proj.shape[0], ctx.status.data_ptr(), _stream()),
+           "kv_write_normed")
+
+
+def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
+                    v_pages: torch.Tensor, block_table: torch.Tensor, items: torch.Tensor,
+                    r1: torch.Tensor, r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
+                    value_dim: int, scale: float, chunk: int, ctx) -> None:
+    """Attention of the step's rows over the pages: q rows of [heads dk] at the front of ``q``
+    (row stride free), out [N, heads dv]; see ``csrc/attention_chunk.cu``."""
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype
+          and out.shape[1] == heads * value_dim, "chunk_attention: q, out and pages")
+    _i32(block_table, "block_table"), _i32(items, "items")
+    _f32(r1, "r1"), _f32(r2, "r2")
+    _need(r1.shape == r2.shape == (heads,), "chunk_attention: r1, r2 [heads]")
+    lib = library.load("attention_chunk")
+    _check(lib.de_attn_chunk(_tag(q.dtype), q.data_ptr(), q.stride(0), out.data_ptr(),
+                             out.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
+                             block_table.data_ptr(), block_table.stride(0), k_pages.shape[0],
+                             ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(),
+                             ctx.seq_qlen.data_ptr(), ctx.seq_pos0.data_ptr(), items.data_ptr(),
+                             items.shape[0], r1.data_ptr(), r2.data_ptr(), heads, kv_heads,
+                             key_dim, value_dim, k_pages.shape[2], float(scale), int(chunk),
+                             ctx.status.data_ptr(), _stream()), "chunk_attention")

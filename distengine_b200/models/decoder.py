@@ -18,11 +18,12 @@ from ..parts.context import CacheBinding, ResidualStream, StepContext, StepPrep
 
 
 def _layer_parts(spec: LayerSpec, dtype: torch.dtype, device: torch.device) -> Block:
-    return build_block(spec.block,
-                       build_mixer(spec.mixer, dtype, device),
-                       build_feed_forward(spec.feed_forward, dtype, device),
-                       build_norm(spec.norm, dtype, device),
-                       build_norm(spec.norm, dtype, device))
+    feed_forward = feed_forward_norm = None
+    if spec.feed_forward is not None:
+        feed_forward = build_feed_forward(spec.feed_forward, dtype, device)
+        feed_forward_norm = build_norm(spec.feed_forward_norm or spec.norm, dtype, device)
+    return build_block(spec.block, build_mixer(spec.mixer, dtype, device), feed_forward,
+                       build_norm(spec.norm, dtype, device), feed_forward_norm)
 
 
 class DecoderModel:

@@ -25,10 +25,25 @@ from .context import CacheBinding, NormAhead, ResidualStream, StepContext, StepP
 @dataclass(frozen=True)
 class PagedKVSpec:
     """Keys and values in pages: [pages, kv_heads, page, head_dim] each.  ``window`` None: every
-    key is kept; a number: only the last ``window`` keys are needed, older pages are given back."""
+    key is kept; a number: only the last ``window`` keys are needed, older pages are given back.
+    ``value_dim``: the values' size where it is not the keys' ([pages, kv_heads, page, value_dim]).
+    ``chunk``: a token reads keys of its own chunk of positions only (chunks of this many
+    positions, counted from 0), so pages that lie wholly before the chunk of the next position are
+    given back."""
     kv_heads: int
     head_dim: int
     window: int | None = None
+    value_dim: int | None = None
+    chunk: int | None = None
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
+
+    @property
+    def releases(self) -> bool:
+        """Whether pages are given back while the request is live."""
+        return self.window is not None or self.chunk is not None
 
 
 @dataclass(frozen=True)
@@ -105,7 +120,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part, NormRider):
-    def cache_spec(self) -> "PagedKVSpec | StateSpec | None":
+    def cache_spec(self) -> "PagedKVSpec | StateSpec | tuple | None":
+        """What the mixer keeps per request: pages of keys and values, a fixed-size state, a
+        tuple of such specs (the run's ``CacheBinding`` then has one binding per member under
+        ``parts``), or nothing."""
         return None
 
     def forward(self, x: torch.Tensor, ctx: StepContext,
@@ -122,15 +140,17 @@ class FeedForward(Part, NormRider):
 class Block:
     """Arrangement of a mixer, a feed-forward and their norms around the residual stream."""
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                 feed_forward_norm: Norm) -> None:
+    def __init__(self, mixer: Mixer, feed_forward: "FeedForward | None", mixer_norm: Norm,
+                 feed_forward_norm: "Norm | None") -> None:
+        """``feed_forward`` and its norm are None in a layer that has a mixer only."""
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
 
     def parts(self) -> dict[str, Part]:
         """role -> part; the roles are the keys of ``LayerSpec.prefixes``."""
-        return {"mixer": self.mixer, "feed_forward": self.feed_forward,
-                "mixer_norm": self.mixer_norm, "feed_forward_norm": self.feed_forward_norm}
+        parts = {"mixer": self.mixer, "feed_forward": self.feed_forward,
+                 "mixer_norm": self.mixer_norm, "feed_forward_norm": self.feed_forward_norm}
+        return {role: part for role, part in parts.items() if part is not None}
 
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: "CacheBinding | None",
                 following: "tuple[Norm, Part] | None" = None) -> None:

@@ -1,6 +1,6 @@
 """Pre-norm block: x += mixer(norm(x)); x += feed_forward(norm(x))
 (src/models/llama.py:66-89).  The sums are carried as the stream's pending branch and folded in
-by the next norm."""
+by the next norm.  A layer without a feed-forward is the first half only."""
 
 from __future__ import annotations
 
@@ -12,12 +12,19 @@ class PreNormBlock(Block):
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: "CacheBinding | None",
                 following=None) -> None:
         h = _normed(self.mixer_norm, stream, ctx)
-        ahead = _ahead(self.mixer, self.feed_forward_norm, self.feed_forward, stream, ctx)
+        if self.feed_forward is None:
+            ahead = None
+            if following is not None:
+                ahead = _ahead(self.mixer, following[0], following[1], stream, ctx)
+        else:
+            ahead = _ahead(self.mixer, self.feed_forward_norm, self.feed_forward, stream, ctx)
         if ahead is None:
             stream.pending = self.mixer.forward(h, ctx, cache)
         else:
             self.mixer.forward(h, ctx, cache, ahead=ahead)
             stream.ahead = ahead
+        if self.feed_forward is None:
+            return
         h = _normed(self.feed_forward_norm, stream, ctx)
         ahead = None
         if following is not None:

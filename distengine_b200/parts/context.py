@@ -84,9 +84,10 @@ class StepPrep:
 class CacheBinding:
     """The cache of one run of a layer.  Paged keys/values: ``k_pages``/``v_pages``
     [pages, kv_heads, page, head_dim] and the group's ``block_table`` [slots, max_pages] (int32,
-    -1 where a request holds no page).  Fixed-size state: ``state`` [slots, *shape].  ``writes``
+    -1 where a request holds no page).  Fixed-size state: ``state`` [slots, *shape].  A mixer
+    whose spec is a tuple gets kind "parts": one binding per member in ``parts``.  ``writes``
     false: this run reads the cache that an earlier run of the plan wrote."""
-    kind: str                                   # "paged" | "state"
+    kind: str                                   # "paged" | "state" | "parts"
     writes: bool = True
     k_pages: "torch.Tensor | None" = None
     v_pages: "torch.Tensor | None" = None
@@ -94,6 +95,7 @@ class CacheBinding:
     page_size: int = 0
     window: "int | None" = None
     state: "torch.Tensor | None" = None
+    parts: "list[CacheBinding] | None" = None
 
 
 @dataclass

@@ -14,8 +14,12 @@ from .context import NormAhead, StepContext, UnscaledRows
 
 class GatedMLP(FeedForward):
     def __init__(self, width: int, inner: int, activation: str, dtype: torch.dtype,
-                 device: torch.device) -> None:
+                 device: torch.device,
+                 names: "tuple[str, str, str]" = ("gate_proj.weight", "up_proj.weight",
+                                                  "down_proj.weight")) -> None:
+        """``names``: the local names of the gate, up and down matrices."""
         super().__init__(dtype, device)
+        self.names = tuple(names)
         if activation != "silu":
             raise ValueError(f"gated_mlp: activation '{activation}' is not implemented; 'silu' is")
         self.width, self.inner = width, inner
@@ -23,14 +27,16 @@ class GatedMLP(FeedForward):
         self.w_down: "torch.Tensor | None" = None
 
     def tensors(self):
-        return {"gate_proj.weight": ((self.inner, self.width), "matrix"),
-                "up_proj.weight": ((self.inner, self.width), "matrix"),
-                "down_proj.weight": ((self.width, self.inner), "matrix")}
+        gate, up, down = self.names
+        return {gate: ((self.inner, self.width), "matrix"),
+                up: ((self.inner, self.width), "matrix"),
+                down: ((self.width, self.inner), "matrix")}
 
     def load(self, tensors):
-        stacked = torch.cat((tensors["gate_proj.weight"], tensors["up_proj.weight"]), dim=0)
+        gate, up, down = self.names
+        stacked = torch.cat((tensors[gate], tensors[up]), dim=0)
         self.w_gate_up = compute_matrix(stacked, self.dtype, self.device)
-        self.w_down = compute_matrix(tensors["down_proj.weight"], self.dtype, self.device)
+        self.w_down = compute_matrix(tensors[down], self.dtype, self.device)
 
     def takes_unscaled(self, n_rows: int) -> bool:
         return ops.norm_ride_parts(n_rows, self.w_gate_up, self.dtype) > 0

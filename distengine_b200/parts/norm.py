@@ -1,8 +1,12 @@
-"""RMS norm with the residual sum folded in.
+"""RMS norm with the residual sum folded in, optionally in groups.
 
 Formula (src/layers/layernorm.py:12-23): float32 mean of squares, x * rsqrt(mean + eps), cast to
 the activation dtype, then times the weight.  The block's residual sums
 (src/models/llama.py:74-89) happen in the same kernel, in 32-bit.
+
+``groups`` > 1: the row is cut into that many equal consecutive parts and each part is divided by
+its own root mean square; the weight still spans the row.  ``tensor``: the local name of the
+weight (architectures differ in it).
 """
 
 from __future__ import annotations
@@ -15,19 +19,23 @@ from .context import NormAhead, ResidualStream, StepContext
 
 
 class RMSNorm(Norm):
-    def __init__(self, width: int, eps: float, dtype: torch.dtype, device: torch.device) -> None:
+    def __init__(self, width: int, eps: float, dtype: torch.dtype, device: torch.device,
+                 groups: int = 1, tensor: str = "weight") -> None:
         super().__init__(dtype, device)
-        self.width, self.eps = width, eps
+        if groups <= 0 or width % groups:
+            raise ValueError(f"rmsnorm: groups ({groups}) must divide the width ({width})")
+        self.width, self.eps, self.groups, self.tensor = width, eps, groups, tensor
         self.weight: "torch.Tensor | None" = None
 
     def tensors(self):
-        return {"weight": ((self.width,), "vector")}
+        return {self.tensor: ((self.width,), "vector")}
 
     def load(self, tensors):
-        self.weight = stored_vector(tensors["weight"], self.dtype, self.device)
+        self.weight = stored_vector(tensors[self.tensor], self.dtype, self.device)
 
     def ahead(self, stream: ResidualStream, ctx: StepContext, count: int):
-        if self.weight.dtype != torch.bfloat16 or stream.pending is not None:
+        if (self.weight.dtype != torch.bfloat16 or stream.pending is not None
+                or self.groups != 1):
             return None
         n = stream.resid.shape[0]
         return NormAhead(self, stream.resid, self.weight, self.eps,
@@ -41,7 +49,8 @@ class RMSNorm(Norm):
                                "result is stream.ahead.result()")
         n_out = stream.resid.shape[0] if rows is None else rows.shape[0]
         out = ctx.buffer(out_name, (n_out, self.width))
-        ops.add_rmsnorm(stream.resid, stream.pending, self.weight, self.eps, out, rows)
+        ops.add_rmsnorm(stream.resid, stream.pending, self.weight, self.eps, out, rows,
+                        groups=self.groups)
         if rows is None:
             stream.pending = None              # it is part of the residual now
         return out

@@ -1,0 +1,85 @@
+"""Mixers side by side: every branch reads the same input, each branch's output is divided by its
+root mean square over the width and multiplied by a weight of its own, and the results are
+averaged.
+
+    out = ( rms_norm(branch_0(x)) * w_0 + rms_norm(branch_1(x)) * w_1 ) / 2
+
+The branches are projected mixers (``parts.recurrent.ProjectedMixer``): their input matrices are
+stacked, so the layer's input goes through one product for all of them.  The mixer's cache spec is
+the tuple of its branches' specs; its run gets one binding per branch.  Branch i's tensors live
+under ``<name_i>.`` and its weight is ``<name_i>.out``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..config.model import PartSpec
+from ..kernels import ops
+from ..kernels import recurrent as rk
+from .base import Mixer, build_mixer, compute_matrix, register_mixer
+from .context import CacheBinding, StepContext, StepPrep
+from .recurrent import ProjectedMixer, stack_segments, vector32
+
+
+class ParallelMixer(Mixer):
+    def __init__(self, width: int, eps: float, branches, dtype: torch.dtype,
+                 device: torch.device) -> None:
+        """``branches``: ((name, PartSpec), (name, PartSpec))."""
+        super().__init__(dtype, device)
+        if len(branches) != 2:
+            raise ValueError("parallel: two branches side by side are implemented")
+        self.width, self.eps = width, eps
+        self.names = [name for name, _ in branches]
+        self.branches = [build_mixer(spec, dtype, device) for _, spec in branches]
+        for branch in self.branches:
+            if not isinstance(branch, ProjectedMixer):
+                raise ValueError("parallel: a branch must be a projected mixer")
+        self.graph_safe = all(branch.graph_safe for branch in self.branches)
+        self.prepare_key = "parallel/" + "+".join(str(getattr(b, "prepare_key", b.kind))
+                                                  for b in self.branches)
+
+    def tensors(self):
+        out = {}
+        for name, branch in zip(self.names, self.branches):
+            for local, what in branch.tensors().items():
+                out[f"{name}.{local}"] = what
+            out[f"{name}.out"] = ((self.width,), "vector")
+        return out
+
+    def load(self, tensors):
+        mats = []
+        for name, branch in zip(self.names, self.branches):
+            branch.load({local: tensors[f"{name}.{local}"] for local in branch.tensors()})
+            mats.append(branch.input_matrix())
+        stacked, self.offsets = stack_segments(mats)
+        self.rows = [m.shape[0] for m in mats]
+        self.w_in = compute_matrix(stacked, self.dtype, self.device)
+        for branch in self.branches:
+            branch.finish_load()
+        self.out_weights = [vector32(tensors[f"{name}.out"], self.device) for name in self.names]
+
+    def cache_spec(self):
+        return tuple(branch.cache_spec() for branch in self.branches)
+
+    def prepare(self, prep: StepPrep) -> None:
+        for branch in self.branches:
+            branch.prepare(prep)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext,
+                cache: "CacheBinding | None") -> torch.Tensor:
+        if cache is None or cache.kind != "parts" or len(cache.parts) != len(self.branches):
+            raise ValueError("parallel: one cache binding per branch is needed")
+        n = x.shape[0]
+        proj = ctx.buffer("parallel.proj", (n, self.w_in.shape[0]))
+        ops.linear(x, self.w_in, out=proj, status=ctx.status)
+        outs = [branch.run(proj[:, at: at + rows], ctx, binding)
+                for branch, at, rows, binding in zip(self.branches, self.offsets, self.rows,
+                                                     cache.parts)]
+        out = ctx.buffer("parallel.out", (n, self.width))
+        rk.mean_of_normed(outs[0], outs[1], self.out_weights[0], self.out_weights[1], out,
+                          self.eps)
+        return out
+
+
+register_mixer("parallel", ParallelMixer)

@@ -1,0 +1,234 @@
+"""Mixers that keep a matrix state per head in their request's slot: the gated delta rule with a
+decay per key channel, and retention.
+
+Both are *projected* mixers (``ProjectedMixer``): everything they take from the layer's input is
+one product against a stacked matrix, so a mixer that runs several of them side by side can stack
+their matrices into one (``parts.parallel``).  The segments of a stacked matrix start at multiples
+of 8 rows (zero rows between them) so that every segment of the product's output can be the
+operand of a further product.
+
+Gated delta rule, per head h with state S [dk, dv] (float32, in the slot):
+
+    q, k, v   = silu(conv(W x))           causal convolution over time per channel, `taps` wide;
+                                          query/key head h // (H / G) serves head h
+    q, k      unit vectors per head (sum of squares + 1e-6 under the root); q also * dk^-1/2
+    beta      = sigmoid(W_b x)            one per head
+    g         = exp(-exp(A_log[h]) * softplus(W_a2 (W_a1 x) + dt_bias))   one per head and key channel
+    S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+    out       = W_o [ o / rms(o) * norm * sigmoid(W_g2 (W_g1 x)) ]        rms over dv, eps inside
+
+Retention, per head with state S [dk, dv]:
+
+    q, k      rotated by position on their first `rotary_dim` features (half-split pairs); k * dk^-1/2
+    S <- decay[h] S + k v^T;  o = S^T q
+    out       = W_o [ o / rms(o) * silu(W_g x) ]
+
+The state, the decays, gates, unit norms, angles and read-outs are float32 in both dtypes; the
+projections and what follows the gate are in the activation dtype.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..kernels import recurrent as rk
+from .base import Mixer, StateSpec, compute_matrix, register_mixer
+from .context import CacheBinding, StepContext
+
+
+def _up8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+def stack_segments(mats: "list[torch.Tensor]") -> "tuple[torch.Tensor, list[int]]":
+    """The matrices one above the other, each starting at a multiple of 8 rows (zero rows fill
+    up); returns the stack and where each starts."""
+    rows, offsets, at = [], [], 0
+    for m in mats:
+        offsets.append(at)
+        rows.append(m)
+        pad = _up8(m.shape[0]) - m.shape[0]
+        if pad:
+            rows.append(m.new_zeros(pad, m.shape[1]))
+        at += m.shape[0] + pad
+    return torch.cat(rows, dim=0), offsets
+
+
+def vector32(t: torch.Tensor, device: torch.device) -> torch.Tensor:
+    return t.to(device=device, dtype=torch.float32).contiguous()
+
+
+class ProjectedMixer(Mixer):
+    """A mixer whose only use of its input is one product: ``input_matrix()`` (host, stored dtype,
+    after ``load``) and ``run(proj, ctx, cache)`` on that product's rows (row stride free)."""
+
+    w_in: "torch.Tensor | None" = None
+
+    def input_matrix(self) -> torch.Tensor:
+        raise NotImplementedError
+
+    def run(self, proj: torch.Tensor, ctx: StepContext, cache: "CacheBinding | None") -> torch.Tensor:
+        raise NotImplementedError
+
+    def finish_load(self) -> None:
+        """Called by whoever owns the input product once the matrix is on the device elsewhere."""
+        self._host_in = None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: "CacheBinding | None") -> torch.Tensor:
+        if self.w_in is None:
+            self.w_in = compute_matrix(self.input_matrix(), self.dtype, self.device)
+            self.finish_load()
+        proj = ctx.buffer(f"{self.kind}.proj", (x.shape[0], self.w_in.shape[0]))
+        ops.linear(x, self.w_in, out=proj, status=ctx.status)
+        return self.run(proj, ctx, cache)
+
+
+class GatedDeltaRule(ProjectedMixer):
+    kind = "gated_delta_rule"
+
+    def __init__(self, width: int, heads: int, kv_heads: int, key_dim: int, value_dim: int,
+                 taps: int, eps: float, dtype: torch.dtype, device: torch.device,
+                 rank: "int | None" = None) -> None:
+        """``rank``: of the two low-rank projections; None: whatever the weight file holds."""
+        super().__init__(dtype, device)
+        if heads % kv_heads:
+            raise ValueError(f"gated_delta_rule: heads ({heads}) must be a multiple of kv_heads "
+                             f"({kv_heads})")
+        if key_dim > rk.max_key_dim():
+            raise ValueError(f"gated_delta_rule: key size {key_dim} is beyond {rk.max_key_dim()}")
+        if taps <= 0:
+            raise ValueError("gated_delta_rule: the convolution needs at least one tap")
+        self.width, self.heads, self.kv_heads = width, heads, kv_heads
+        self.dk, self.dv, self.taps, self.eps, self.rank = key_dim, value_dim, taps, eps, rank
+        self.channels = 2 * kv_heads * key_dim + heads * value_dim
+        self.state_rows = heads * key_dim * value_dim
+
+    def tensors(self):
+        d, r = self.width, -1 if self.rank is None else self.rank
+        qk, hv, hk = self.kv_heads * self.dk, self.heads * self.dv, self.heads * self.dk
+        return {"q": ((qk, d), "matrix"), "q.conv": ((qk, self.taps), "matrix"),
+                "k": ((qk, d), "matrix"), "k.conv": ((qk, self.taps), "matrix"),
+                "v": ((hv, d), "matrix"), "v.conv": ((hv, self.taps), "matrix"),
+                "b": ((self.heads, d), "matrix"), "A_log": ((self.heads,), "vector"),
+                "norm": ((self.dv,), "vector"),
+                "a1": ((r, d), "matrix"), "a2": ((hk, r), "matrix"),
+                "dt_bias": ((hk,), "vector"),
+                "g1": ((r, d), "matrix"), "g2": ((hv, r), "matrix"),
+                "o": ((d, hv), "matrix")}
+
+    def load(self, tensors):
+        if not (tensors["a1"].shape[0] == tensors["a2"].shape[1]
+                and tensors["g1"].shape[0] == tensors["g2"].shape[1]):
+            raise ValueError("gated_delta_rule: the two halves of a low-rank projection do not "
+                             "have the same rank")
+        self._host_in, offsets = stack_segments([
+            torch.cat((tensors["q"], tensors["k"], tensors["v"]), dim=0),
+            tensors["b"], tensors["a1"], tensors["g1"]])
+        _, self.b_col, self.a_col, self.g_col = offsets
+        self.a_rank, self.g_rank = tensors["a1"].shape[0], tensors["g1"].shape[0]
+        self.w_a2 = compute_matrix(tensors["a2"], self.dtype, self.device)
+        self.w_g2 = compute_matrix(tensors["g2"], self.dtype, self.device)
+        self.w_o = compute_matrix(tensors["o"], self.dtype, self.device)
+        self.conv = vector32(torch.cat((tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]),
+                                       dim=0), self.device)
+        self.a_log = vector32(tensors["A_log"], self.device)
+        self.dt_bias = vector32(tensors["dt_bias"], self.device)
+        self.norm = vector32(tensors["norm"], self.device)
+        self.w_in = None
+
+    def input_matrix(self) -> torch.Tensor:
+        return self._host_in
+
+    def cache_spec(self):
+        # the state matrices, then the convolution's last taps - 1 inputs
+        return StateSpec((self.state_rows + (self.taps - 1) * self.channels,), torch.float32)
+
+    def run(self, proj, ctx, cache):
+        if cache is None or cache.kind != "state":
+            raise ValueError("the gated delta rule needs a state slot")
+        if not cache.writes:
+            raise ValueError("the gated delta rule cannot read another run's state: it advances it")
+        n, f32 = proj.shape[0], torch.float32
+        H, G, dk, dv = self.heads, self.kv_heads, self.dk, self.dv
+        a = ctx.buffer("delta.a", (n, H * dk), f32)
+        ops.linear(proj[:, self.a_col: self.a_col + self.a_rank], self.w_a2, out=a,
+                   out_dtype=f32, status=ctx.status)
+        gate = ctx.buffer("delta.gate", (n, H * dv), f32)
+        ops.linear(proj[:, self.g_col: self.g_col + self.g_rank], self.w_g2, out=gate,
+                   out_dtype=f32, status=ctx.status)
+        qn = ctx.buffer("delta.q", (n, G * dk), f32)
+        kn = ctx.buffer("delta.k", (n, G * dk), f32)
+        vv = ctx.buffer("delta.v", (n, H * dv), f32)
+        beta = ctx.buffer("delta.beta", (n, H), f32)
+        gdec = ctx.buffer("delta.g", (n, H * dk), f32)
+        rk.delta_prep(proj, a, self.conv, self.dt_bias, self.a_log, cache.state, self.state_rows,
+                      ctx, qn, kn, vv, beta, gdec, H, G, dk, dv, self.b_col)
+        rk.conv_state(proj, cache.state, self.state_rows, self.channels, self.taps, ctx)
+        o = ctx.buffer("delta.o", (n, H * dv), f32)
+        rk.state_scan(qn, kn, vv, cache.state, o, H, G, dk, dv, ctx, g=gdec, beta=beta)
+        gated = ctx.buffer("delta.gated", (n, H * dv))
+        rk.head_gate(o, gate, self.norm, gated, H, dv, self.eps)
+        out = ctx.buffer("delta.out", (n, self.width))
+        ops.linear(gated, self.w_o, out=out, status=ctx.status)
+        return out
+
+
+class Retention(ProjectedMixer):
+    kind = "retention"
+
+    def __init__(self, width: int, heads: int, key_dim: int, value_dim: int, decay, rotary_dim: int,
+                 theta: float, eps: float, dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__(dtype, device)
+        if len(decay) != heads:
+            raise ValueError(f"retention: {len(decay)} decays for {heads} heads")
+        if rotary_dim % 2 or not 0 <= rotary_dim <= key_dim:
+            raise ValueError(f"retention: rotary_dim ({rotary_dim}) must be even and at most the "
+                             f"key size ({key_dim})")
+        if key_dim > rk.max_key_dim():
+            raise ValueError(f"retention: key size {key_dim} is beyond {rk.max_key_dim()}")
+        self.width, self.heads, self.dk, self.dv, self.eps = width, heads, key_dim, value_dim, eps
+        self.rotary_dim = rotary_dim
+        self.decay = torch.tensor([float(x) for x in decay], dtype=torch.float32, device=device)
+        indices = torch.arange(0, rotary_dim, 2, dtype=torch.float64)
+        self.inv_freq = (float(theta) ** (-indices / max(rotary_dim, 1))).to(torch.float32).to(device)
+
+    def tensors(self):
+        d, hk, hv = self.width, self.heads * self.dk, self.heads * self.dv
+        return {"q": ((hk, d), "matrix"), "k": ((hk, d), "matrix"), "v": ((hv, d), "matrix"),
+                "g": ((hv, d), "matrix"), "o": ((d, hv), "matrix")}
+
+    def load(self, tensors):
+        self._host_in, offsets = stack_segments([torch.cat((tensors["q"], tensors["k"]), dim=0),
+                                                 tensors["v"], tensors["g"]])
+        _, self.v_col, self.g_col = offsets
+        self.w_o = compute_matrix(tensors["o"], self.dtype, self.device)
+        self.w_in = None
+
+    def input_matrix(self) -> torch.Tensor:
+        return self._host_in
+
+    def cache_spec(self):
+        return StateSpec((self.heads * self.dk * self.dv,), torch.float32)
+
+    def run(self, proj, ctx, cache):
+        if cache is None or cache.kind != "state":
+            raise ValueError("retention needs a state slot")
+        if not cache.writes:
+            raise ValueError("retention cannot read another run's state: it advances it")
+        n, f32, H, dk, dv = proj.shape[0], torch.float32, self.heads, self.dk, self.dv
+        qr = ctx.buffer("retention.q", (n, H * dk), f32)
+        kr = ctx.buffer("retention.k", (n, H * dk), f32)
+        rk.retention_prep(proj, self.inv_freq, self.rotary_dim, H, dk, qr, kr, ctx)
+        o = ctx.buffer("retention.o", (n, H * dv), f32)
+        rk.state_scan(qr, kr, proj[:, self.v_col: self.v_col + H * dv], cache.state, o, H, H, dk,
+                      dv, ctx, decay=self.decay)
+        gated = ctx.buffer("retention.gated", (n, H * dv))
+        rk.head_gate(o, proj[:, self.g_col: self.g_col + H * dv], None, gated, H, dv, self.eps)
+        out = ctx.buffer("retention.out", (n, self.width))
+        ops.linear(gated, self.w_o, out=out, status=ctx.status)
+        return out
+
+
+register_mixer("gated_delta_rule", GatedDeltaRule)
+register_mixer("retention", Retention)

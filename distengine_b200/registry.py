@@ -1,4 +1,5 @@
-"""One registry from the architecture's name (config.json ``architectures[0]``) to its model.
+"""One registry from the architecture's name (config.json ``architectures[0]``, or the string
+under ``architecture``) to its model.
 
 An entry holds the typed configuration's parser and the function that builds the model from it.
 The reference has no registry: it constructs ``LlamaForCausalLM`` directly
@@ -45,9 +46,11 @@ def resolve(config_json: Mapping[str, Any]) -> tuple[Architecture, ModelConfig]:
     """The architecture entry and the parsed configuration for a config.json."""
     _ensure_builtin()
     names = config_json.get("architectures")
+    if names is None and isinstance(config_json.get("architecture"), str):
+        names = [config_json["architecture"]]
     if not isinstance(names, list) or not names or not isinstance(names[0], str):
         raise ConfigError("config.json: key 'architectures' must be a list with the model "
-                          "class's name")
+                          "class's name (or 'architecture' its name)")
     name = names[0]
     if name not in _ARCHITECTURES:
         raise ConfigError(f"config.json: architecture '{name}' is not registered; known: "

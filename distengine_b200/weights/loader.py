@@ -67,6 +67,12 @@ def stored_dtype_policy(tensor: torch.Tensor, dtype: torch.dtype) -> torch.Tenso
     return tensor.to(torch.int32)
 
 
+def _fits(shape, wanted) -> bool:
+    """Whether a stored shape is the wanted one; -1 in ``wanted`` stands for a size that the file
+    itself gives (the part checks such sizes against each other when it takes the tensors)."""
+    return len(shape) == len(wanted) and all(w == -1 or s == w for s, w in zip(shape, wanted))
+
+
 def load_checked(model_dir: str, expected: dict[str, tuple[int, ...]],
                  optional: set[str] = frozenset(), dtype: torch.dtype = torch.bfloat16,
                  integer: set[str] = frozenset()) -> dict[str, torch.Tensor]:
@@ -87,7 +93,7 @@ def load_checked(model_dir: str, expected: dict[str, tuple[int, ...]],
                 error.unexpected.append(name)
                 continue
             shape = handle.shape(name)
-            if tuple(shape) != tuple(expected[name]):
+            if not _fits(shape, expected[name]):
                 error.wrong_shape.append((name, tuple(expected[name]), tuple(shape)))
                 continue
             stored = handle.dtype(name)

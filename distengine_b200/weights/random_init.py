@@ -30,6 +30,10 @@ def random_tensors(expected: dict[str, tuple[int, ...]], vectors: set[str], seed
     generator.manual_seed(seed)
     out: dict[str, torch.Tensor] = {}
     for name, shape in expected.items():
+        if any(size < 0 for size in shape):
+            raise ValueError(f"tensor '{name}' has a size that only a weight file gives "
+                             f"({list(shape)}); name it in the configuration to draw random "
+                             f"weights")
         if name in vectors:
             if norm_init == "ones":
                 value = torch.ones(shape, dtype=torch.float32)
