@@ -219,11 +219,13 @@ class CacheManager:
         return self.paged[0].pool.num_pages if self.paged else 0
 
     def num_free_pages(self) -> int:
-        """Free pages of the fullest group."""
-        return min((g.pool.num_free for g in self.paged), default=0)
+        """Free pages of the fullest group (without a paged group nothing ever runs out)."""
+        return min((g.pool.num_free for g in self.paged), default=1 << 30)
 
     @property
     def capacity_tokens(self) -> int:
+        if not self.paged:                    # fixed-size state only: the slots are the limit
+            return self.max_len
         return self.num_pages * self.page_size
 
     # ------------------------------------------------------------------ requests

@@ -2,6 +2,10 @@
 only, in float64 (or float32) on the CPU.  It shares no code with the engine: the engine's parts
 and kernels are compared with it.
 
+``act`` (None or torch.bfloat16) models the engine's bfloat16 mode: the results of matrix
+products, the norms' outputs, the gated rows and the cached values are rounded to it (``rnd``);
+the residual stream, the states, scores, weights, decays, gates and unit norms are not.
+
 Notation: T tokens, width D.  A weight matrix is stored [out, in]; ``lin`` applies it.  ``w`` maps
 tensor names to tensors, ``config`` is the parsed config.json.
 """
@@ -13,8 +17,12 @@ import math
 import torch
 
 
-def lin(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    return x @ weight.to(x.dtype).t()
+def rnd(x: torch.Tensor, act) -> torch.Tensor:
+    return x if act is None else x.to(act).to(x.dtype)
+
+
+def lin(x: torch.Tensor, weight: torch.Tensor, act=None) -> torch.Tensor:
+    return rnd(x @ weight.to(x.dtype).t(), act)
 
 
 def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
@@ -22,12 +30,13 @@ def rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
 
 
-def grouped_rms_norm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
+def grouped_rms_norm(x: torch.Tensor, weight: torch.Tensor, groups: int, eps: float,
+                     act=None) -> torch.Tensor:
     """The last axis is cut into ``groups`` equal consecutive parts; each part is normalised by its
     own root mean square; the whole is multiplied by the weight."""
     shape = x.shape
     parts = x.reshape(*shape[:-1], groups, shape[-1] // groups)
-    return rms(parts, eps).reshape(shape) * weight.to(x.dtype)
+    return rnd(rnd(rms(parts, eps).reshape(shape), act) * weight.to(x.dtype), act)
 
 
 def silu(x: torch.Tensor) -> torch.Tensor:
@@ -70,36 +79,36 @@ def gated_delta_rule(q, k, v, beta, g):
     return out
 
 
-def channel_delta_mixer(h, w, p, m, eps):
+def channel_delta_mixer(h, w, p, m, eps, act=None):
     """The 'channel_delta' mixer on h [T, D]; tensors under prefix p, sizes in m."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = silu(causal_conv(lin(h, w[p + "q"]), w[p + "q.conv"]))
-    k = silu(causal_conv(lin(h, w[p + "k"]), w[p + "k.conv"]))
-    v = silu(causal_conv(lin(h, w[p + "v"]), w[p + "v.conv"]))
+    q = silu(causal_conv(lin(h, w[p + "q"], act), w[p + "q.conv"]))
+    k = silu(causal_conv(lin(h, w[p + "k"], act), w[p + "k.conv"]))
+    v = silu(causal_conv(lin(h, w[p + "v"], act), w[p + "v.conv"]))
     rep = H // G
     q = unit(q.view(T, G, dk)).repeat_interleave(rep, dim=1) * dk ** -0.5
     k = unit(k.view(T, G, dk)).repeat_interleave(rep, dim=1)
     v = v.view(T, H, dv)
-    beta = torch.sigmoid(lin(h, w[p + "b"]))
-    a = lin(lin(h, w[p + "a1"]), w[p + "a2"]) + w[p + "dt_bias"].to(h.dtype)
+    beta = torch.sigmoid(lin(h, w[p + "b"], act))
+    a = lin(lin(h, w[p + "a1"], act), w[p + "a2"]) + w[p + "dt_bias"].to(h.dtype)
     rate = torch.exp(w[p + "A_log"].to(h.dtype))
     g = torch.exp(-rate[None, :, None] * softplus(a).view(T, H, dk))
     o = gated_delta_rule(q, k, v, beta, g)
-    gate = torch.sigmoid(lin(lin(h, w[p + "g1"]), w[p + "g2"])).view(T, H, dv)
-    o = rms(o, eps) * w[p + "norm"].to(h.dtype) * gate
-    return lin(o.reshape(T, H * dv), w[p + "o"])
+    gate = torch.sigmoid(lin(lin(h, w[p + "g1"], act), w[p + "g2"])).view(T, H, dv)
+    o = rnd(rms(o, eps) * w[p + "norm"].to(h.dtype) * gate, act)
+    return lin(o.reshape(T, H * dv), w[p + "o"], act)
 
 
-def chunked_bias_attention(h, w, p, m, eps):
+def chunked_bias_attention(h, w, p, m, eps, act=None):
     """Softmax attention inside chunks of positions, with a logarithmic distance penalty and
     normalised values."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     size, scale = m["mask"]["size"], m["scale"]
-    q = lin(h, w[p + "q"]).view(T, H, dk)
-    k = lin(h, w[p + "k"]).view(T, G, dk).repeat_interleave(H // G, dim=1)
-    v = rms(lin(h, w[p + "v"]).view(T, G, dv), eps).repeat_interleave(H // G, dim=1)
+    q = lin(h, w[p + "q"], act).view(T, H, dk)
+    k = lin(h, w[p + "k"], act).view(T, G, dk).repeat_interleave(H // G, dim=1)
+    v = rnd(rms(lin(h, w[p + "v"], act).view(T, G, dv), eps), act).repeat_interleave(H // G, dim=1)
     pos = torch.arange(T)
     dist = (pos[:, None] - pos[None, :]).clamp(min=0).to(h.dtype)
     r1, r2 = w[p + "r1"].to(h.dtype), w[p + "r2"].to(h.dtype)
@@ -107,8 +116,8 @@ def chunked_bias_attention(h, w, p, m, eps):
     scores = scores - r1[:, None, None] * torch.log1p(r2[:, None, None] * dist[None])
     seen = (pos[None, :] <= pos[:, None]) & ((pos[None, :] // size) == (pos[:, None] // size))
     scores = scores.masked_fill(~seen[None], float("-inf"))
-    o = torch.einsum("hij,jhd->ihd", torch.softmax(scores, dim=-1), v)
-    return lin(o.reshape(T, H * dv), w[p + "o"])
+    o = rnd(torch.einsum("hij,jhd->ihd", torch.softmax(scores, dim=-1), v), act)
+    return lin(o.reshape(T, H * dv), w[p + "o"], act)
 
 
 def rotate_half_layout(x, dims, base):
@@ -134,47 +143,52 @@ def retention(q, k, v, decay):
     return out
 
 
-def retention_mixer(h, w, p, m, eps):
+def retention_mixer(h, w, p, m, eps, act=None):
     T = h.shape[0]
     H, dk, dv = m["heads"], m["dim"], m["vdim"]
-    q = rotate_half_layout(lin(h, w[p + "q"]).view(T, H, dk), m["rot"]["dims"], m["rot"]["base"])
-    k = rotate_half_layout(lin(h, w[p + "k"]).view(T, H, dk), m["rot"]["dims"], m["rot"]["base"])
+    q = rotate_half_layout(lin(h, w[p + "q"], act).view(T, H, dk), m["rot"]["dims"],
+                           m["rot"]["base"])
+    k = rotate_half_layout(lin(h, w[p + "k"], act).view(T, H, dk), m["rot"]["dims"],
+                           m["rot"]["base"])
     k = k * dk ** -0.5
-    v = lin(h, w[p + "v"]).view(T, H, dv)
+    v = lin(h, w[p + "v"], act).view(T, H, dv)
     o = retention(q, k, v, torch.tensor(m["decay"], dtype=h.dtype))
-    o = rms(o, eps).reshape(T, H * dv) * silu(lin(h, w[p + "g"]))
-    return lin(o, w[p + "o"])
+    o = rnd(rms(o, eps).reshape(T, H * dv) * silu(lin(h, w[p + "g"], act)), act)
+    return lin(o, w[p + "o"], act)
 
 
-def parallel_mixer(h, w, p, m, eps):
-    left = chunked_bias_attention(h, w, p + "left.", m["left"], eps)
-    right = retention_mixer(h, w, p + "right.", m["right"], eps)
-    return 0.5 * (rms(left, eps) * w[p + "left.out"].to(h.dtype)
-                  + rms(right, eps) * w[p + "right.out"].to(h.dtype))
+def parallel_mixer(h, w, p, m, eps, act=None):
+    left = chunked_bias_attention(h, w, p + "left.", m["left"], eps, act)
+    right = retention_mixer(h, w, p + "right.", m["right"], eps, act)
+    return rnd(0.5 * (rms(left, eps) * w[p + "left.out"].to(h.dtype)
+                      + rms(right, eps) * w[p + "right.out"].to(h.dtype)), act)
 
 
-def dense_feed_forward(h, w, p):
-    return lin(silu(lin(h, w[p + "gate"])) * lin(h, w[p + "up"]), w[p + "down"])
+def dense_feed_forward(h, w, p, act=None):
+    # (the engine's fused products keep gate and up in 32-bit up to the activation)
+    gate, up = lin(h, w[p + "gate"]), lin(h, w[p + "up"])
+    return lin(rnd(silu(gate) * up, act), w[p + "down"], act)
 
 
 MIXERS = {"channel_delta": channel_delta_mixer, "parallel": parallel_mixer}
 
 
-def forward(config: dict, w: dict, ids: list[int], dtype=torch.float64, layers_out=None):
+def forward(config: dict, w: dict, ids: list[int], dtype=torch.float64, layers_out=None,
+            act=None):
     """Logits [T, vocab] of one whole sequence; ``layers_out`` (a list) receives the residual
-    stream after every layer."""
+    stream after every layer; ``act``: see the module's header."""
     eps, groups = config["norm"]["eps"], config["norm"]["groups"]
     x = w["embed"].to(dtype)[torch.tensor(ids)]
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
-        h = grouped_rms_norm(x, w[p + "norm1"], groups, eps)
-        x = x + MIXERS[layer["type"]](h, w, p + "mix.", layer["mixer"], eps)
+        h = grouped_rms_norm(x, w[p + "norm1"], groups, eps, act)
+        x = x + MIXERS[layer["type"]](h, w, p + "mix.", layer["mixer"], eps, act)
         if layer.get("mlp") is not None:
-            h = grouped_rms_norm(x, w[p + "norm2"], groups, eps)
-            x = x + dense_feed_forward(h, w, p + "mlp.")
+            h = grouped_rms_norm(x, w[p + "norm2"], groups, eps, act)
+            x = x + dense_feed_forward(h, w, p + "mlp.", act)
         if layers_out is not None:
             layers_out.append(x.clone())
-    x = grouped_rms_norm(x, w["final.norm"], groups, eps)
+    x = grouped_rms_norm(x, w["final.norm"], groups, eps, act)
     return lin(x, w["head"])
 
 
