@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload headline|mixed|long|fp32] [--layers L]
+                    [--workload headline|mixed|long|fp32|vomotar] [--layers L]
 
 The default (``headline``) has the TinyLlama-1.1B layer sizes in bfloat16.  A step is one decode
 step of a batch of 8 requests whose prompts of 512 tokens are in the cache; K steps are timed with
@@ -30,6 +30,10 @@ Other workloads, each with its own line (the number of layers is named beside th
 * ``long``: Llama-3-8B layer sizes (vocabulary 128,256), 64 requests with prompts of 4,096 tokens:
   prompt portions of 4,096 tokens and decode steps at batch 64 over the long cache.
 * ``fp32``: the headline's sizes in the true 32-bit path (decode at batch 8, prefill of 2,048).
+* ``vomotar``: the Vomotar architecture (layers of gated delta rule, and of chunk-masked attention
+  beside retention) at the headline's width, feed-forward and vocabulary, beside the Llama decoder
+  with the same number of layers: decode at batch 8 and 64 and a prompt of 2,048 tokens for both,
+  and every kernel that is the design's own, alone, against its roofline.
 """
 
 from __future__ import annotations
@@ -354,6 +358,203 @@ def workload_fp32(args, warmup: int, steps: int) -> int:
     return 0
 
 
+def vomotar_shape(layers: int) -> dict:
+    """A Vomotar model of the headline's width, feed-forward and vocabulary: every fourth layer
+    runs chunk-masked attention beside retention, the others the gated delta rule."""
+    delta = {"type": "channel_delta",
+             "mixer": {"heads": 16, "kv_heads": 16, "dim": 128, "vdim": 128, "conv": 4,
+                       "rank": 64},
+             "mlp": {"kind": "dense", "ff": MODEL["intermediate_size"]}}
+    parallel = {"type": "parallel",
+                "mixer": {"left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128,
+                                   "scale": 128 ** -0.5, "mask": {"size": 1024}},
+                          "right": {"heads": 8, "dim": 128, "vdim": 256,
+                                    "decay": [1.0 - 2.0 ** -(5 + i) for i in range(8)],
+                                    "rot": {"dims": 64, "base": 10000.0}}},
+                "mlp": {"kind": "dense", "ff": MODEL["intermediate_size"]}}
+    return {"architecture": "Vomotar", "vocab": MODEL["vocab_size"],
+            "width": MODEL["hidden_size"], "norm": {"eps": 1e-5, "groups": 1},
+            "layers": [parallel if i % 4 == 0 else delta for i in range(layers)]}
+
+
+def vomotar_folder(layers: int) -> str:
+    from distengine_b200.weights import write_random_model
+    folder = os.path.join(tempfile.gettempdir(), f"distengine_b200-bench-{os.getuid()}",
+                          f"vomotar-shape-{layers}-layers-seed0-bf16")
+    marker = os.path.join(folder, ".complete")
+    if not os.path.isfile(marker):
+        print("[bench] writing the random-weights model folder ...", file=sys.stderr, flush=True)
+        write_random_model(vomotar_shape(layers), folder, seed=0, dtype="bfloat16",
+                           norm_init="uniform")
+        with open(marker, "w") as handle:
+            handle.write("ok")
+    return folder
+
+
+def vomotar_kernels(peak: dict) -> list[dict]:
+    """The design's own kernels alone, at the sizes of ``vomotar_shape``, for a prompt of 2,048
+    tokens and for a decode step of 64 sequences: microseconds (CUDA events, L2 flushed before
+    every launch), the bytes or flops they cannot avoid, and that against the measured peaks."""
+    from types import SimpleNamespace
+    import numpy as np
+    import torch
+    from distengine_b200.kernels import recurrent as rk
+    from distengine_b200.kernels.attention_plan import build_plan
+    dev, bf16, f32 = "cuda:0", torch.bfloat16, torch.float32
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fp32_peak = 148 * 128 * 2 * 1.965e9          # fused multiply-adds of the CUDA cores
+
+    def ctx_of(lens, pos0):
+        lens = np.asarray(lens, dtype=np.int32)
+        pos0 = np.asarray(pos0, dtype=np.int32)
+        qstart = (np.cumsum(lens) - lens).astype(np.int32)
+        seq = np.repeat(np.arange(len(lens), dtype=np.int32), lens)
+        slots = np.arange(len(lens), dtype=np.int32)
+        pos = pos0[seq] + np.arange(lens.sum(), dtype=np.int32) - qstart[seq]
+        d = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+        return SimpleNamespace(n_seqs=len(lens), token_seq=d(seq), token_slot=d(slots[seq]),
+                               positions=d(pos), seq_slot=d(slots), seq_qstart=d(qstart),
+                               seq_qlen=d(lens), seq_pos0=d(pos0),
+                               host=SimpleNamespace(seq_qlen=lens, seq_pos0=pos0),
+                               status=torch.zeros(1, dtype=torch.int32, device=dev))
+
+    def timed(fn, repeats=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(repeats):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(times)
+
+    out = []
+
+    def record(name, case, us, bytes_=0, flops=0):
+        entry = {"kernel": name, "case": case, "us": round(us, 1)}
+        hbm_us = bytes_ / (peak["hbm_gbs"] * 1e3)
+        fma_us = flops / fp32_peak * 1e6
+        entry["roofline_us"] = round(max(hbm_us, fma_us), 1)
+        entry["bound"] = "hbm" if hbm_us >= fma_us else "fp32 fma"
+        entry["frac"] = round(max(hbm_us, fma_us) / us, 3)
+        out.append(entry)
+
+    H, dk, dv, K, width = 16, 128, 128, 4, MODEL["hidden_size"]
+    for case, lens, pos0 in (("prompt of 2,048", [2048], [0]), ("decode, 64 sequences", [1] * 64,
+                                                                 [600] * 64)):
+        ctx = ctx_of(lens, pos0)
+        n, s = int(sum(lens)), len(lens)
+        C = 2 * H * dk + H * dv
+        proj = torch.randn(n, C + 16 + 128, device=dev).to(bf16)
+        a = torch.randn(n, H * dk, device=dev)
+        gate = torch.randn(n, H * dv, device=dev)
+        taps = torch.randn(C, K, device=dev)
+        state = torch.zeros(s, H * dk * dv + (K - 1) * C, device=dev)
+        qn, kn, vv = (torch.empty(n, H * dk, device=dev) for _ in range(3))
+        beta, gdec = torch.empty(n, H, device=dev), torch.empty(n, H * dk, device=dev)
+        vec = torch.randn(H * dk, device=dev)
+        us = timed(lambda: rk.delta_prep(proj, a, taps, vec, vec[:H].contiguous(), state,
+                                         H * dk * dv, ctx, qn, kn, vv, beta, gdec, H, H, dk, dv, C))
+        record("delta_prep", case, us, bytes_=n * (C * 2 + H * dk * 4 + (4 * H * dk) * 4))
+        o = torch.empty(n, H * dv, device=dev)
+        us = timed(lambda: rk.state_scan(qn, kn, vv, state, o, H, H, dk, dv, ctx, g=gdec, beta=beta))
+        record("state_scan (delta rule)", case, us, bytes_=2 * s * H * dk * dv * 4 + n * 5 * H * dk * 4,
+               flops=n * H * dk * dv * 8)
+        gated = torch.empty(n, H * dv, dtype=bf16, device=dev)
+        us = timed(lambda: rk.head_gate(o, gate, vec[:dv].contiguous(), gated, H, dv, 1e-5))
+        record("head_gate", case, us, bytes_=n * H * dv * (4 + 4 + 2))
+        # retention: 8 heads of 128 x 256
+        RH, rdv = 8, 256
+        rproj = torch.randn(n, 2 * RH * dk + 2 * RH * rdv, device=dev).to(bf16)
+        rstate = torch.zeros(s, RH * dk * rdv, device=dev)
+        qr, kr = torch.empty(n, RH * dk, device=dev), torch.empty(n, RH * dk, device=dev)
+        inv = torch.rand(32, device=dev)
+        us = timed(lambda: rk.retention_prep(rproj, inv, 64, RH, dk, qr, kr, ctx))
+        record("retention_prep", case, us, bytes_=n * 2 * RH * dk * (2 + 4))
+        ro = torch.empty(n, RH * rdv, device=dev)
+        decay = torch.full((RH,), 0.99, device=dev)
+        us = timed(lambda: rk.state_scan(qr, kr, rproj[:, 2 * RH * dk: 2 * RH * dk + RH * rdv],
+                                         rstate, ro, RH, RH, dk, rdv, ctx, decay=decay))
+        record("state_scan (retention)", case, us,
+               bytes_=2 * s * RH * dk * rdv * 4 + n * (2 * RH * dk * 4 + RH * rdv * 6),
+               flops=n * RH * dk * rdv * 5)
+        # chunk attention: 16 heads on 4 kv heads, chunk 1,024
+        AH, G, chunk, page = 16, 4, 1024, 16
+        longest = max(p + l for p, l in zip(pos0, lens))
+        pages_seq = (longest + page - 1) // page
+        kp = torch.randn(s * pages_seq, G, page, dk, device=dev).to(bf16)
+        vp = torch.randn(s * pages_seq, G, page, dv, device=dev).to(bf16)
+        table = torch.arange(s * pages_seq, dtype=torch.int32, device=dev).view(s, pages_seq)
+        aproj = torch.randn(n, AH * dk + G * (dk + dv), device=dev).to(bf16)
+        us = timed(lambda: rk.kv_write_normed(aproj, AH * dk, G, dk, dv, 1e-5, kp, vp, table, ctx))
+        record("kv_write_normed", case, us, bytes_=n * G * (dk + dv) * 4)
+        plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, AH // G, G,
+                          rk.chunk_rows_per_tile(), 0, chunk=0)
+        items = torch.from_numpy(plan.items).to(dev)
+        ao = torch.empty(n, AH * dv, dtype=bf16, device=dev)
+        r = torch.rand(AH, device=dev)
+        us = timed(lambda: rk.chunk_attention(aproj, ao, kp, vp, table, items, r, r, AH, G, dk, dv,
+                                              0.09, chunk, ctx))
+        keys = sum(sum(min(p + i, (p + i) % chunk) + 1 for i in range(l))
+                   for p, l in zip(pos0, lens))
+        record("chunk_attention", case, us,
+               bytes_=sum(min(p + l, chunk + l) for p, l in zip(pos0, lens)) * G * (dk + dv) * 2,
+               flops=keys * AH * (dk + dv))
+        x1 = torch.randn(n, width, device=dev).to(bf16)
+        x2 = torch.randn(n, width, device=dev).to(bf16)
+        w32 = torch.rand(width, device=dev)
+        mo = torch.empty(n, width, dtype=bf16, device=dev)
+        us = timed(lambda: rk.mean_of_normed(x1, x2, w32, w32, mo, 1e-5))
+        record("mean_of_normed", case, us, bytes_=n * width * 6)
+    return out
+
+
+def workload_vomotar(args, warmup: int, steps: int) -> int:
+    """Vomotar beside Llama at equal width, feed-forward, vocabulary and number of layers."""
+    import numpy as np
+    import torch
+    from distengine_b200 import Engine, EngineConfig
+    peak, peak_kind = peaks()
+    layers = args.layers
+    rng = np.random.default_rng(0)
+    vocab = MODEL["vocab_size"]
+    result = {}
+    for name, folder in (("vomotar", vomotar_folder(layers)), ("llama", model_folder(layers))):
+        pages = (64 * (PROMPT + 8 + warmup + steps) + PREFILL) // PAGE + 64
+        engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=pages,
+                                             decode_batch_size=64, max_batch_tokens=PREFILL,
+                                             max_model_len=4096, use_graphs=not args.no_graphs))
+        prefill_ms, prefill_step_ms = timed_prefill(engine, PREFILL, rng, vocab, repeats=5)
+        entry = {"prefill_2048": {"ms": round(prefill_ms, 3),
+                                  "ms_with_host_prepare": round(prefill_step_ms, 3),
+                                  "tokens_per_s": round(PREFILL / prefill_ms * 1e3, 1)}}
+        for batch in (8, 64):
+            ms, launches, _, clocks = timed_decode(engine, batch, PROMPT, steps, warmup, rng, vocab)
+            entry[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4),
+                                         "tokens_per_s": round(batch / ms * 1e3, 1),
+                                         "gpu_launches": int(launches), "clocks": clocks}
+        result[name] = entry
+        del engine
+        torch.cuda.empty_cache()
+    mine = result["vomotar"]["decode_b8"]
+    print(json.dumps({
+        "metric": "decode tokens/s at batch 8, Vomotar at the TinyLlama-1.1B width",
+        "value": mine["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": mine["ms_per_step"], "dtype": "bf16",
+        "higher_is_better": True, "data": "synthetic", "impl": "ours", "workload": "vomotar",
+        "config": {"layers": layers, "width": MODEL["hidden_size"],
+                   "ff": MODEL["intermediate_size"], "vocab": vocab, "seq_len": PROMPT,
+                   "page_size": PAGE, "peaks": peak_kind, "shape": vomotar_shape(4)["layers"][:2],
+                   "l2": "weights larger than L2 are read every step; kernels alone: L2 flushed"},
+        "gpu_launches": mine["gpu_launches"], "clocks": mine["clocks"],
+        "models": result, "kernels": vomotar_kernels(peak)}))
+    return 0
+
+
 def workload_long(args, warmup: int, steps: int) -> int:
     """Llama-3-8B layer sizes: 64 requests with prompts of 4,096 tokens (fed as portions of 4,096
     tokens), then decode steps at batch 64 over the long cache; vocabulary 128,256."""
@@ -555,9 +756,9 @@ def main() -> int:
                         help="print one decode step's in-kernel timeline (kernels built with "
                              "DISTENGINE_B200_DEFINES=DE_TRACE)")
     parser.add_argument("--workload", default="headline",
-                        choices=["headline", "mixed", "long", "fp32"])
+                        choices=["headline", "mixed", "long", "fp32", "vomotar"])
     args = parser.parse_args()
-    if args.workload in ("mixed", "long") and "--layers" not in " ".join(sys.argv):
+    if args.workload in ("mixed", "long", "vomotar") and "--layers" not in " ".join(sys.argv):
         args.layers = 8          # of the 32 that the Llama-2-7B and Llama-3-8B shapes have
 
     if args.gpus != 1:
@@ -569,8 +770,8 @@ def main() -> int:
     if args.timeline:
         return timeline(args)
     if args.workload != "headline":
-        return {"mixed": workload_mixed, "long": workload_long,
-                "fp32": workload_fp32}[args.workload](args, warmup, steps)
+        return {"mixed": workload_mixed, "long": workload_long, "fp32": workload_fp32,
+                "vomotar": workload_vomotar}[args.workload](args, warmup, steps)
 
     import numpy as np
     import torch
