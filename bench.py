@@ -492,13 +492,13 @@ def vomotar_kernels(peak: dict) -> list[dict]:
         aproj = torch.randn(n, AH * dk + G * (dk + dv), device=dev).to(bf16)
         us = timed(lambda: rk.kv_write_normed(aproj, AH * dk, G, dk, dv, 1e-5, kp, vp, table, ctx))
         record("kv_write_normed", case, us, bytes_=n * G * (dk + dv) * 4)
-        plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, AH // G, G,
-                          rk.chunk_rows_per_tile(), 0, chunk=0)
+        rows = rk.chunk_rows_per_tile(bf16, dk, dv, n > s)
+        plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, AH // G, G, rows, 0, chunk=0)
         items = torch.from_numpy(plan.items).to(dev)
         ao = torch.empty(n, AH * dv, dtype=bf16, device=dev)
         r = torch.rand(AH, device=dev)
         us = timed(lambda: rk.chunk_attention(aproj, ao, kp, vp, table, items, r, r, AH, G, dk, dv,
-                                              0.09, chunk, ctx))
+                                              0.09, chunk, ctx, tile_rows=rows))
         keys = sum(sum(min(p + i, (p + i) % chunk) + 1 for i in range(l))
                    for p, l in zip(pos0, lens))
         record("chunk_attention", case, us,

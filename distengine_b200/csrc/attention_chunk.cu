@@ -177,9 +177,248 @@ attn_chunk_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, in
     }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// The same attention for key and value rows that are whole 16-byte pieces (sizes that are a
+// multiple of 8 in bfloat16, of 4 in float32): the next tile of keys and values is asked for in
+// 16-byte loads into registers before the current one is worked on, a warp takes RW rows (it
+// reads a key or a value from shared memory once for all of them), and shared memory is read as
+// float4.  A row's sums are formed in the same order as in the kernel above whatever RW is.
+// ------------------------------------------------------------------------------------------
+template <typename T> struct Piece;                 // 16 bytes of T as floats
+template <> struct Piece<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+        f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y);
+        f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+    }
+};
+template <> struct Piece<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+        const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+template <typename T, int RW, int NCH>
+__global__ void __launch_bounds__(ROWS * 32)
+attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+                      const T* __restrict__ k_pages, const T* __restrict__ v_pages,
+                      const int* __restrict__ block_table, int table_stride, int num_pages,
+                      const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
+                      const int* __restrict__ seq_qlen, const int* __restrict__ seq_pos0,
+                      const WorkItem* __restrict__ items, const float* __restrict__ r1,
+                      const float* __restrict__ r2, int heads, int kv_heads, int dk, int dv,
+                      int page, float scale, int chunk, int* __restrict__ status) {
+    constexpr int PN = Piece<T>::N;
+    extern __shared__ __align__(16) float smem[];
+    const int ks = ((dk + 31) / 32) * 32 + 4;       // a key's stride: float4 reads without conflicts
+    float* Ks = smem;                                // [TILE][ks]
+    float* Vs = Ks + TILE * ks;                      // [TILE][dv]
+    float* Qs = Vs + TILE * dv;                      // [ROWS * RW][dk]
+    float* Held = Qs + ROWS * RW * dk;               // [TILE]: 0, or -inf for a key without a page
+
+    const WorkItem it = items[blockIdx.x];
+    if (it.kv_begin >= it.kv_end) {
+        pdl_wait();
+        return;
+    }
+    const int hk = blockIdx.y;
+    const int g = heads / kv_heads;
+    const int qlen = seq_qlen[it.seq], pos0 = seq_pos0[it.seq];
+    const int slot = seq_slot[it.seq], tok0 = seq_qstart[it.seq];
+    const int rows_total = qlen * g;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    bool active[RW];
+    int tok[RW], hq[RW], pos[RW], row_lo[RW], row_hi[RW];
+    float pen1[RW], pen2[RW], m[RW], l[RW];
+    bool any = false;
+#pragma unroll
+    for (int i = 0; i < RW; ++i) {
+        const int r = it.row0 + warp * RW + i;
+        active[i] = r < rows_total;
+        any |= active[i];
+        tok[i] = active[i] ? r / g : 0;
+        hq[i] = hk * g + (active[i] ? r % g : 0);
+        pos[i] = pos0 + tok[i];
+        pen1[i] = r1[hq[i]];
+        pen2[i] = r2[hq[i]];
+        row_lo[i] = it.kv_begin;
+        if (chunk > 0) row_lo[i] = max(row_lo[i], pos[i] / chunk * chunk);
+        row_hi[i] = min(it.kv_end, pos[i] + 1);
+        m[i] = -INFINITY;
+        l[i] = 0.0f;
+    }
+    const int last_row = min(it.row0 + ROWS * RW, rows_total) - 1;
+    const int max_pos = pos0 + last_row / g, min_pos = pos0 + it.row0 / g;
+    const int k_hi = min(it.kv_end, max_pos + 1);
+    int k_lo_true = it.kv_begin;
+    if (chunk > 0) k_lo_true = max(k_lo_true, min_pos / chunk * chunk);
+    const int k_lo = (k_lo_true / TILE) * TILE;
+
+    const int ck = dk / PN, cv = dv / PN, per_key = ck + cv;
+    uint4 pre[NCH];
+    unsigned missing = 0;                            // bit c: piece c's key has no page
+
+    pdl_wait();
+    auto prefetch = [&](int kt) {
+        missing = 0;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+            const int e = threadIdx.x + c * (ROWS * 32);
+            pre[c] = make_uint4(0u, 0u, 0u, 0u);
+            if (e >= TILE * per_key) continue;
+            const int j = e / per_key, w = e - j * per_key;
+            const int kpos = kt + j;
+            if (kpos < k_lo_true || kpos >= k_hi) continue;
+            const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
+            if (page_id < 0 || page_id >= num_pages) {
+                missing |= 1u << c;
+                continue;
+            }
+            const size_t at = ((size_t)page_id * kv_heads + hk) * page + (size_t)(kpos % page);
+            const T* src = w < ck ? k_pages + at * dk + w * PN : v_pages + at * dv + (w - ck) * PN;
+            pre[c] = *reinterpret_cast<const uint4*>(src);
+        }
+    };
+    prefetch(k_lo);
+#pragma unroll
+    for (int i = 0; i < RW; ++i)
+        for (int d = lane; d < dk; d += 32)
+            Qs[(warp * RW + i) * dk + d] =
+                active[i] ? to_float(q[(size_t)(tok0 + tok[i]) * q_stride + hq[i] * dk + d]) : 0.0f;
+
+    float acc[RW][MAX_D / 128][4];
+#pragma unroll
+    for (int i = 0; i < RW; ++i)
+#pragma unroll
+        for (int b = 0; b < MAX_D / 128; ++b)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][b][e] = 0.0f;
+
+    for (int kt = k_lo; kt < k_hi; kt += TILE) {
+        __syncthreads();                             // the tile before this one has been used
+#pragma unroll
+        for (int c = 0; c < NCH; ++c) {
+            const int e = threadIdx.x + c * (ROWS * 32);
+            if (e >= TILE * per_key) continue;
+            const int j = e / per_key, w = e - j * per_key;
+            float f[PN];
+            Piece<T>::unpack(pre[c], f);
+            float* dst = w < ck ? Ks + j * ks + w * PN : Vs + j * dv + (w - ck) * PN;
+#pragma unroll
+            for (int x = 0; x < PN; x += 4)
+                *reinterpret_cast<float4*>(dst + x) = make_float4(f[x], f[x + 1], f[x + 2], f[x + 3]);
+            if (w == 0) {
+                const bool gone = (missing >> c) & 1u;
+                Held[j] = gone ? -INFINITY : 0.0f;
+                if (gone && status != nullptr) atomicExch(status, 2);
+            }
+        }
+        __syncthreads();
+        if (kt + TILE < k_hi) prefetch(kt + TILE);   // in flight while this tile is worked on
+        if (!any) continue;
+
+        const int kpos = kt + lane;
+        const float4* kr = reinterpret_cast<const float4*>(Ks + lane * ks);
+        float s[RW];
+#pragma unroll
+        for (int i = 0; i < RW; ++i) s[i] = 0.0f;
+        for (int d = 0; d < dk / 4; ++d) {
+            const float4 kk = kr[d];
+#pragma unroll
+            for (int i = 0; i < RW; ++i) {
+                const float4 qq = reinterpret_cast<const float4*>(Qs + (warp * RW + i) * dk)[d];
+                s[i] = fmaf(qq.x, kk.x, s[i]);
+                s[i] = fmaf(qq.y, kk.y, s[i]);
+                s[i] = fmaf(qq.z, kk.z, s[i]);
+                s[i] = fmaf(qq.w, kk.w, s[i]);
+            }
+        }
+        const bool held = Held[lane] == 0.0f;
+        float p[RW];
+        bool some = false;
+#pragma unroll
+        for (int i = 0; i < RW; ++i) {
+            const bool valid = active[i] && kpos >= row_lo[i] && kpos < row_hi[i] && held;
+            const float sc = valid ? s[i] * scale - pen1[i] * log1pf(pen2[i] * (float)(pos[i] - kpos))
+                                   : -INFINITY;
+            const float m_new = fmaxf(m[i], warp_max(sc));
+            if (m_new == -INFINITY) {               // nothing of this tile is visible to the row
+                p[i] = 0.0f;
+                continue;
+            }
+            p[i] = valid ? expf(sc - m_new) : 0.0f;
+            const float corr = expf(m[i] - m_new);
+            l[i] = l[i] * corr + warp_sum(p[i]);
+#pragma unroll
+            for (int b = 0; b < MAX_D / 128; ++b)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[i][b][e] *= corr;
+            m[i] = m_new;
+            some = true;
+        }
+        if (!some) continue;
+        for (int j = 0; j < TILE; ++j) {
+            float pj[RW];
+            bool zero = true;
+#pragma unroll
+            for (int i = 0; i < RW; ++i) {
+                pj[i] = __shfl_sync(0xffffffffu, p[i], j);
+                zero &= pj[i] == 0.0f;
+            }
+            if (zero) continue;                      // the same for the whole warp
+#pragma unroll
+            for (int b = 0; b < MAX_D / 128; ++b) {
+                const int dd = 4 * lane + 128 * b;
+                if (dd < dv) {
+                    const float4 vv = *reinterpret_cast<const float4*>(Vs + j * dv + dd);
+#pragma unroll
+                    for (int i = 0; i < RW; ++i) {
+                        if (pj[i] == 0.0f) continue;  // as the kernel above skips it
+                        acc[i][b][0] = fmaf(pj[i], vv.x, acc[i][b][0]);
+                        acc[i][b][1] = fmaf(pj[i], vv.y, acc[i][b][1]);
+                        acc[i][b][2] = fmaf(pj[i], vv.z, acc[i][b][2]);
+                        acc[i][b][3] = fmaf(pj[i], vv.w, acc[i][b][3]);
+                    }
+                }
+            }
+        }
+    }
+    pdl_trigger();
+#pragma unroll
+    for (int i = 0; i < RW; ++i) {
+        if (!active[i]) continue;
+        const float inv = l[i] > 0.0f ? 1.0f / l[i] : 0.0f;
+        T* o = out + (size_t)(tok0 + tok[i]) * out_stride + hq[i] * dv;
+#pragma unroll
+        for (int b = 0; b < MAX_D / 128; ++b) {
+            const int dd = 4 * lane + 128 * b;
+            if (dd < dv) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o[dd + e] = from_float<T>(acc[i][b][e] * inv);
+            }
+        }
+    }
+}
+
 }  // namespace
 
-DE_EXPORT int de_attn_chunk_rows() { return ROWS; }
+// rows of a tile: 8, or 32 when the step brings prompt portions (`wide`) and the sizes allow the
+// kernel that gives a warp four rows
+static bool vec_ok(int dtype, int dk, int dv) {
+    const int pn = dtype == DE_BF16 ? 8 : 4;
+    return dk % pn == 0 && dv % pn == 0 && dk <= MAX_D && dv <= MAX_D;
+}
+DE_EXPORT int de_attn_chunk_rows(int dtype, int dk, int dv, int wide) {
+    return vec_ok(dtype, dk, dv) && wide ? ROWS * 4 : ROWS;
+}
 
 DE_EXPORT int de_kv_write_normed(int dtype, const void* proj, int ld, int k_col,
                                  const int* positions, const int* token_slot, int G, int dk,
@@ -206,10 +445,49 @@ DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, i
                             const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
                             const int* items, int num_items, const float* r1, const float* r2,
                             int heads, int kv_heads, int dk, int dv, int page, float scale,
-                            int chunk, int* status, void* stream) {
+                            int chunk, int tile_rows, int* status, void* stream) {
     if (num_items <= 0) return 0;
     if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D || heads % kv_heads != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
+    if (tile_rows != ROWS && !(tile_rows == ROWS * 4 && vec_ok(dtype, dk, dv))) return -5;
+    if (vec_ok(dtype, dk, dv) && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0) {
+        const int rw = tile_rows / ROWS;
+        const int pn = dtype == DE_BF16 ? 8 : 4;
+        const int pieces = TILE * (dk / pn + dv / pn);
+        const int nch = (pieces + ROWS * 32 - 1) / (ROWS * 32);
+        const size_t vsmem = (size_t)(TILE * (((dk + 31) / 32) * 32 + 4) + TILE * dv +
+                                      ROWS * rw * dk + TILE) * sizeof(float);
+        dim3 vgrid(num_items, kv_heads);
+#define VEC(T, RW, NCH)                                                                         \
+    do {                                                                                        \
+        if (vsmem > 48 * 1024) {                                                                \
+            cudaError_t ve = cudaFuncSetAttribute(attn_chunk_vec_kernel<T, RW, NCH>,            \
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                                  (int)vsmem);                                  \
+            if (ve != cudaSuccess) return (int)ve;                                              \
+        }                                                                                       \
+        return de_launch(attn_chunk_vec_kernel<T, RW, NCH>, vgrid, dim3(ROWS * 32), vsmem, s,   \
+                         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages,         \
+                         (const T*)v_pages, block_table, table_stride, num_pages, seq_slot,     \
+                         seq_qstart, seq_qlen, seq_pos0, (const WorkItem*)items, r1, r2, heads, \
+                         kv_heads, dk, dv, page, scale, chunk, status);                         \
+    } while (0)
+#define VEC_N(T, RW)                                                                            \
+    do {                                                                                        \
+        if (nch <= 2) VEC(T, RW, 2);                                                            \
+        if (nch <= 4) VEC(T, RW, 4);                                                            \
+        if (nch <= 8) VEC(T, RW, 8);                                                            \
+        VEC(T, RW, 16);                                                                         \
+    } while (0)
+        if (dtype == DE_BF16) {
+            if (rw == 4) VEC_N(__nv_bfloat16, 4);
+            VEC_N(__nv_bfloat16, 1);
+        }
+        if (rw == 4) VEC_N(float, 4);
+        VEC_N(float, 1);
+#undef VEC_N
+#undef VEC
+    }
     const size_t smem = (size_t)(TILE * (dk + 1) + TILE * dv + ROWS * dk) * sizeof(float);
     dim3 grid(num_items, kv_heads);
     cudaError_t e;

@@ -151,30 +151,47 @@ __global__ void retention_prep_kernel(const T* __restrict__ proj, int ld,
 
 // ------------------------------------------------------------------------------------------
 // The scan.  grid (sequences, heads, column blocks of COLS); thread = 4 * column + quarter.
-// Row i of the state belongs to quarter i % 4, register i / 4; in shared memory a token's vector
-// lies quarter by quarter (quarter l at l * (R + 4)), so a quarter reads its share as float4 and
-// the four quarters of a warp hit different banks.
+// Rows of the state go to the quarters four at a time: row i belongs to quarter (i / 4) % 4,
+// register 4 * (i / 16) + i % 4; in shared memory a token's vector lies quarter by quarter
+// (quarter l at l * (R + 4)), so four consecutive rows are 16 bytes there as in memory (one
+// cp.async), a quarter reads its share as float4 and the four quarters of a warp hit different
+// banks.  COLS is 32, or less when a step has so few (sequence, head) pairs that blocks of 32
+// columns would leave most SMs idle.  Block (s, 0, 0) also moves the slot's kept convolution
+// inputs on (`conv_*`; the kernel before this one has read the old ones).
 // ------------------------------------------------------------------------------------------
-constexpr int COLS = 32;
 constexpr int TB = 8;          // tokens whose vectors are in flight together
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
-template <typename VT, int R, bool DELTA>
+struct ConvKeep {              // the convolution inputs a slot keeps (K <= 1: nothing to do)
+    const void* proj;
+    int ld, bf16, offset, C, K;
+};
+
+__device__ __forceinline__ int state_row(int r, int l) {      // register r of quarter l -> row
+    return ((r >> 2) << 4) + (l << 2) + (r & 3);
+}
+
+template <typename VT, int R, bool DELTA, int COLS>
 __global__ void __launch_bounds__(COLS * 4)
 scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
             const VT* __restrict__ v, int ldv, const float* __restrict__ g, int ldg,
             const float* __restrict__ beta, int ldb, const float* __restrict__ decay,
             float* __restrict__ state, long long slot_stride, float* __restrict__ out,
             const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
-            const int* __restrict__ seq_qlen, int H, int rep, int dk, int dv) {
+            const int* __restrict__ seq_qlen, int H, int rep, int dk, int dv, int vec16,
+            ConvKeep keep) {
     constexpr int PD = 4 * (R + 4);                  // a token's vector in shared memory
     constexpr int VECS = DELTA ? 3 : 2;              // q, k (, g)
     extern __shared__ __align__(16) float buf[];     // [2][TB][VECS][PD]
@@ -187,11 +204,25 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
     __syncthreads();                                 // the padding stays zero from here on
     pdl_wait();
 
-    float* S_g = state + (size_t)seq_slot[s] * slot_stride + (size_t)h * dk * dv;
+    float* slot_state = state + (size_t)seq_slot[s] * slot_stride;
+    if (keep.K > 1 && h == 0 && blockIdx.z == 0) {
+        float* cs = slot_state + keep.offset;
+        for (int c = threadIdx.x; c < keep.C; c += COLS * 4)
+            for (int i = 0; i < keep.K - 1; ++i) {   // ascending: what is read lies ahead
+                const int rel = qlen - (keep.K - 1) + i;
+                float x;
+                if (rel < 0) x = cs[(size_t)(i + qlen) * keep.C + c];
+                else if (keep.bf16)
+                    x = __bfloat162float(((const __nv_bfloat16*)keep.proj)[(size_t)(tok0 + rel) * keep.ld + c]);
+                else x = ((const float*)keep.proj)[(size_t)(tok0 + rel) * keep.ld + c];
+                cs[(size_t)i * keep.C + c] = x;
+            }
+    }
+    float* S_g = slot_state + (size_t)h * dk * dv;
     float S[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = 4 * r + l;
+        const int i = state_row(r, l);
         S[r] = (live && i < dk) ? S_g[(size_t)i * dv + col] : 0.0f;
     }
     const float dec = DELTA ? 0.0f : decay[h];
@@ -199,31 +230,57 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
     auto issue = [&](int b) {
         float* dst = buf + (size_t)(b & 1) * TB * VECS * PD;
         const int count = min(TB, qlen - b * TB);
-        for (int idx = threadIdx.x; idx < count * dk; idx += COLS * 4) {
-            const int t = idx / dk, i = idx - t * dk;
-            const size_t tok = (size_t)(tok0 + b * TB + t);
-            float* d = dst + (size_t)t * VECS * PD + (i & 3) * (R + 4) + (i >> 2);
-            cp_async4(d, q + tok * ldq + hk * dk + i);
-            cp_async4(d + PD, k + tok * ldk + hk * dk + i);
-            if (DELTA) cp_async4(d + 2 * PD, g + tok * ldg + h * dk + i);
+        if (vec16) {
+            const int quads = dk >> 2;
+            for (int idx = threadIdx.x; idx < count * quads; idx += COLS * 4) {
+                const int t = idx / quads, c = idx - t * quads;
+                const size_t tok = (size_t)(tok0 + b * TB + t);
+                float* d = dst + (size_t)t * VECS * PD + (c & 3) * (R + 4) + ((c >> 2) << 2);
+                cp_async16(d, q + tok * ldq + hk * dk + 4 * c);
+                cp_async16(d + PD, k + tok * ldk + hk * dk + 4 * c);
+                if (DELTA) cp_async16(d + 2 * PD, g + tok * ldg + h * dk + 4 * c);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < count * dk; idx += COLS * 4) {
+                const int t = idx / dk, i = idx - t * dk;
+                const size_t tok = (size_t)(tok0 + b * TB + t);
+                float* d = dst + (size_t)t * VECS * PD + ((i >> 2) & 3) * (R + 4) +
+                           ((i >> 4) << 2) + (i & 3);
+                cp_async4(d, q + tok * ldq + hk * dk + i);
+                cp_async4(d + PD, k + tok * ldk + hk * dk + i);
+                if (DELTA) cp_async4(d + 2 * PD, g + tok * ldg + h * dk + i);
+            }
         }
         cp_async_commit();
     };
-
-    const int batches = (qlen + TB - 1) / TB;
-    if (batches > 0) issue(0);
-    for (int b = 0; b < batches; ++b) {
+    // a batch's values and gates do not depend on the state: they are asked for a batch ahead
+    float nv[TB], nb[TB];
+    auto fetch = [&](int b) {
         const int count = min(TB, qlen - b * TB);
-        // this batch's values and gates: loads that do not depend on the state, asked for early
-        float vt[TB], bt[TB];
 #pragma unroll
         for (int t = 0; t < TB; ++t) {
             const size_t tok = (size_t)(tok0 + b * TB + t);
-            vt[t] = (live && t < count) ? to_float(v[tok * ldv + h * dv + col]) : 0.0f;
-            bt[t] = (DELTA && t < count) ? beta[tok * ldb + h] : 0.0f;
+            nv[t] = (live && t < count) ? to_float(v[tok * ldv + h * dv + col]) : 0.0f;
+            nb[t] = (DELTA && t < count) ? beta[tok * ldb + h] : 0.0f;
+        }
+    };
+
+    const int batches = (qlen + TB - 1) / TB;
+    if (batches > 0) {
+        issue(0);
+        fetch(0);
+    }
+    for (int b = 0; b < batches; ++b) {
+        const int count = min(TB, qlen - b * TB);
+        float vt[TB], bt[TB];
+#pragma unroll
+        for (int t = 0; t < TB; ++t) {
+            vt[t] = nv[t];
+            bt[t] = nb[t];
         }
         if (b + 1 < batches) {
             issue(b + 1);
+            fetch(b + 1);
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -283,7 +340,7 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
     if (live) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            const int i = 4 * r + l;
+            const int i = state_row(r, l);
             if (i < dk) S_g[(size_t)i * dv + col] = S[r];
         }
     }
@@ -347,30 +404,68 @@ __global__ void mean_of_normed_kernel(const T* __restrict__ a, const T* __restri
     }
 }
 
-template <typename VT, bool DELTA>
-int launch_scan(int R, dim3 grid, cudaStream_t s, const float* q, int ldq, const float* k, int ldk,
-                const VT* v, int ldv, const float* g, int ldg, const float* beta, int ldb,
-                const float* decay, float* state, long long slot_stride, float* out,
-                const int* seq_slot, const int* seq_qstart, const int* seq_qlen, int H, int rep,
-                int dk, int dv) {
+template <typename VT, bool DELTA, int COLS>
+int launch_scan_cols(int R, dim3 grid, cudaStream_t s, const float* q, int ldq, const float* k,
+                     int ldk, const VT* v, int ldv, const float* g, int ldg, const float* beta,
+                     int ldb, const float* decay, float* state, long long slot_stride, float* out,
+                     const int* seq_slot, const int* seq_qstart, const int* seq_qlen, int H,
+                     int rep, int dk, int dv, int vec16, ConvKeep keep) {
 #define SCAN(RR)                                                                                \
     do {                                                                                        \
         const size_t smem = (size_t)2 * TB * (DELTA ? 3 : 2) * 4 * (RR + 4) * sizeof(float);    \
         if (smem > 48 * 1024) {                                                                 \
-            cudaError_t e = cudaFuncSetAttribute(scan_kernel<VT, RR, DELTA>,                    \
+            cudaError_t e = cudaFuncSetAttribute(scan_kernel<VT, RR, DELTA, COLS>,              \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                                  (int)smem);                                    \
             if (e != cudaSuccess) return (int)e;                                                \
         }                                                                                       \
-        return de_launch(scan_kernel<VT, RR, DELTA>, grid, dim3(COLS * 4), smem, s, q, ldq, k,  \
-                         ldk, v, ldv, g, ldg, beta, ldb, decay, state, slot_stride, out,        \
-                         seq_slot, seq_qstart, seq_qlen, H, rep, dk, dv);                       \
+        return de_launch(scan_kernel<VT, RR, DELTA, COLS>, grid, dim3(COLS * 4), smem, s, q,    \
+                         ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, slot_stride,     \
+                         out, seq_slot, seq_qstart, seq_qlen, H, rep, dk, dv, vec16, keep);     \
     } while (0)
     if (R <= 8) SCAN(8);
     if (R <= 16) SCAN(16);
     if (R <= 32) SCAN(32);
     SCAN(64);
 #undef SCAN
+}
+
+int sm_count() {
+    static int count = 0;
+    if (count == 0) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess ||
+            cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+            count = 148;
+    }
+    return count;
+}
+
+template <typename VT, bool DELTA>
+int launch_scan(cudaStream_t s, const float* q, int ldq, const float* k, int ldk, const VT* v,
+                int ldv, const float* g, int ldg, const float* beta, int ldb, const float* decay,
+                float* state, long long slot_stride, float* out, const int* seq_slot,
+                const int* seq_qstart, const int* seq_qlen, int n_seqs, int H, int rep, int dk,
+                int dv, ConvKeep keep) {
+    // rows go to the quarters in fours, sixteen at a time: a quarter holds 4 * ceil(dk / 16)
+    const int R = 4 * ((dk + 15) / 16);
+    const int vec16 = (dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && (!DELTA || ldg % 4 == 0) &&
+                       (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 &&
+                       (!DELTA || (uintptr_t)g % 16 == 0)) ? 1 : 0;
+    // narrower blocks while blocks of 32 columns would not give every SM two
+    int cols = 32;
+    while (cols > 8 && (long long)n_seqs * H * ((dv + cols - 1) / cols) < 2LL * sm_count())
+        cols >>= 1;
+    if (dv <= 8) cols = 8; else if (dv <= 16 && cols > 16) cols = 16;
+    dim3 grid(n_seqs, H, (dv + cols - 1) / cols);
+#define COLS_CASE(CC)                                                                           \
+    return launch_scan_cols<VT, DELTA, CC>(R, grid, s, q, ldq, k, ldk, v, ldv, g, ldg, beta,    \
+                                           ldb, decay, state, slot_stride, out, seq_slot,      \
+                                           seq_qstart, seq_qlen, H, rep, dk, dv, vec16, keep)
+    if (cols == 8) COLS_CASE(8);
+    if (cols == 16) COLS_CASE(16);
+    COLS_CASE(32);
+#undef COLS_CASE
 }
 
 }  // namespace
@@ -426,32 +521,35 @@ DE_EXPORT int de_retention_prep(int dtype, const void* proj, int ld, const int* 
 }
 
 // v_dtype: the type of v (DE_F32 for the delta rule, whose values come from its own preparation).
-// delta 1: g [N, ldg] and beta [N, ldb] are used; 0: decay [H].
+// delta 1: g [N, ldg] and beta [N, ldb] are used; 0: decay [H].  conv_taps > 1: the slots also
+// keep the last conv_taps - 1 rows of the first conv_channels columns of conv_proj (of type
+// conv_dtype, row stride conv_ld) at conv_offset of their state row.
 DE_EXPORT int de_state_scan(int delta, int v_dtype, const float* q, int ldq, const float* k,
                             int ldk, const void* v, int ldv, const float* g, int ldg,
                             const float* beta, int ldb, const float* decay, float* state,
                             long long slot_stride, float* out, const int* seq_slot,
                             const int* seq_qstart, const int* seq_qlen, int n_seqs, int H, int rep,
-                            int dk, int dv, void* stream) {
+                            int dk, int dv, const void* conv_proj, int conv_ld, int conv_dtype,
+                            int conv_offset, int conv_channels, int conv_taps, void* stream) {
     if (n_seqs <= 0) return 0;
     if (dk <= 0 || dk > 256 || dv <= 0 || H <= 0 || rep <= 0 || H % rep) return -2;
     cudaStream_t s = (cudaStream_t)stream;
-    const int R = (dk + 3) / 4;
-    dim3 grid(n_seqs, H, (dv + COLS - 1) / COLS);
+    ConvKeep keep = {conv_proj, conv_ld, conv_dtype == DE_BF16 ? 1 : 0, conv_offset,
+                     conv_channels, conv_proj ? conv_taps : 0};
     if (delta) {
         if (v_dtype != DE_F32) return -4;
-        return launch_scan<float, true>(R, grid, s, q, ldq, k, ldk, (const float*)v, ldv, g, ldg,
-                                        beta, ldb, decay, state, slot_stride, out, seq_slot,
-                                        seq_qstart, seq_qlen, H, rep, dk, dv);
+        return launch_scan<float, true>(s, q, ldq, k, ldk, (const float*)v, ldv, g, ldg, beta,
+                                        ldb, decay, state, slot_stride, out, seq_slot, seq_qstart,
+                                        seq_qlen, n_seqs, H, rep, dk, dv, keep);
     }
     if (v_dtype == DE_BF16)
-        return launch_scan<__nv_bfloat16, false>(R, grid, s, q, ldq, k, ldk,
-                                                 (const __nv_bfloat16*)v, ldv, g, ldg, beta, ldb,
-                                                 decay, state, slot_stride, out, seq_slot,
-                                                 seq_qstart, seq_qlen, H, rep, dk, dv);
-    return launch_scan<float, false>(R, grid, s, q, ldq, k, ldk, (const float*)v, ldv, g, ldg,
-                                     beta, ldb, decay, state, slot_stride, out, seq_slot,
-                                     seq_qstart, seq_qlen, H, rep, dk, dv);
+        return launch_scan<__nv_bfloat16, false>(s, q, ldq, k, ldk, (const __nv_bfloat16*)v, ldv,
+                                                 g, ldg, beta, ldb, decay, state, slot_stride, out,
+                                                 seq_slot, seq_qstart, seq_qlen, n_seqs, H, rep,
+                                                 dk, dv, keep);
+    return launch_scan<float, false>(s, q, ldq, k, ldk, (const float*)v, ldv, g, ldg, beta, ldb,
+                                     decay, state, slot_stride, out, seq_slot, seq_qstart,
+                                     seq_qlen, n_seqs, H, rep, dk, dv, keep);
 }
 
 DE_EXPORT int de_head_gate(int dtype, const float* o, const void* gate, int ld_gate,

@@ -63,10 +63,10 @@ SIGNATURES: dict[str, dict[str, list]] = {
                         P],
     },
     "attention_chunk": {
-        "de_attn_chunk_rows": [],
+        "de_attn_chunk_rows": [I, I, I, I],
         "de_kv_write_normed": [I, P, I, I, P, P, I, I, I, F, P, P, P, I, I, I, I, P, P],
         "de_attn_chunk": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, I, F,
-                          I, P, P],
+                          I, I, P, P],
     },
     "recurrent": {
         "de_recurrent_max_key_dim": [],
@@ -75,7 +75,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_conv_state": [I, P, I, P, L, I, P, P, P, I, I, I, P],
         "de_retention_prep": [I, P, I, P, P, I, I, I, P, P, I, P],
         "de_state_scan": [I, I, P, I, P, I, P, I, P, I, P, I, P, P, L, P, P, P, P, I, I, I, I, I,
-                          P],
+                          P, I, I, I, I, I, P],
         "de_head_gate": [I, P, P, I, P, P, I, I, I, F, I, P],
         "de_mean_of_normed": [I, P, P, P, P, P, I, I, F, P],
     },

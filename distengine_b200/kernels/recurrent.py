@@ -91,12 +91,15 @@ def retention_prep(proj: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, 
 def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor,
                out: torch.Tensor, heads: int, qk_heads: int, key_dim: int, value_dim: int, ctx,
                g: "torch.Tensor | None" = None, beta: "torch.Tensor | None" = None,
-               decay: "torch.Tensor | None" = None) -> None:
+               decay: "torch.Tensor | None" = None, keep: "tuple | None" = None) -> None:
     """Walk every sequence's tokens of the step through its state ``state`` [slots, >= H dk dv]
     (float32, rows [h][key channel][value channel] at the front) and write the read-outs, float32
     [N, H dv].  With ``g`` [N, H dk] and ``beta`` [N, H]: the delta rule with a decay per key
     channel.  With ``decay`` [H]: retention.  q, k float32 [N, qk_heads dk]; v [N, H dv] in
-    float32 or the activation dtype (any row stride)."""
+    float32 or the activation dtype (any row stride).  ``keep`` = (proj, offset, channels, taps):
+    the slots also keep, at ``offset`` of their rows, the last ``taps - 1`` rows of the first
+    ``channels`` columns of ``proj`` of every sequence (a convolution's inputs, as ``conv_state``
+    does; the kernel before this one has read the old ones)."""
     n = q.shape[0]
     delta = g is not None
     _need(delta != (decay is not None) and (beta is not None) == delta,
@@ -118,6 +121,13 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
     else:
         _f32(decay, "decay")
         _need(decay.shape == (heads,) and decay.is_contiguous(), "state_scan: decay [H]")
+    conv = (None, 0, 0, 0, 0, 0)
+    if keep is not None:
+        proj, offset, channels, taps = keep
+        _need(proj.stride(1) == 1 and proj.shape == (n, proj.shape[1]) and proj.shape[1] >= channels
+              and offset + (taps - 1) * channels <= state.shape[1],
+              "state_scan: the kept convolution inputs do not fit")
+        conv = (proj.data_ptr(), proj.stride(0), _tag(proj.dtype), offset, channels, taps)
     lib = library.load("recurrent")
     _check(lib.de_state_scan(int(delta), _tag(v.dtype), q.data_ptr(), q.stride(0), k.data_ptr(),
                              k.stride(0), v.data_ptr(), v.stride(0), _ptr(g),
@@ -125,7 +135,8 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
                              beta.stride(0) if delta else 0, _ptr(decay), state.data_ptr(),
                              state.stride(0), out.data_ptr(), ctx.seq_slot.data_ptr(),
                              ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, heads,
-                             heads // qk_heads, key_dim, value_dim, _stream()), "state_scan")
+                             heads // qk_heads, key_dim, value_dim, *conv, _stream()),
+           "state_scan")
 
 
 def head_gate(o: torch.Tensor, gate: torch.Tensor, weight: "torch.Tensor | None",
@@ -164,8 +175,11 @@ def mean_of_normed(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch
 
 
 # ------------------------------------------------------------------------------- chunk attention
-def chunk_rows_per_tile() -> int:
-    return int(library.load("attention_chunk").de_attn_chunk_rows())
+def chunk_rows_per_tile(dtype: torch.dtype, key_dim: int, value_dim: int, wide: bool) -> int:
+    """Rows of a tile of the chunk attention: 8, or 32 for steps with prompt portions (``wide``)
+    at sizes whose rows are whole 16-byte pieces."""
+    return int(library.load("attention_chunk").de_attn_chunk_rows(_tag(dtype), key_dim, value_dim,
+                                                                  int(wide)))
 
 
 def kv_write_normed(proj: torch.Tensor, k_col: int, kv_heads: int, key_dim: int, value_dim: int,
@@ -193,9 +207,10 @@ def kv_write_normed(proj: torch.Tensor, k_col: int, kv_heads: int, key_dim: int,
 def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
                     v_pages: torch.Tensor, block_table: torch.Tensor, items: torch.Tensor,
                     r1: torch.Tensor, r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
-                    value_dim: int, scale: float, chunk: int, ctx) -> None:
+                    value_dim: int, scale: float, chunk: int, ctx, tile_rows: int = 8) -> None:
     """Attention of the step's rows over the pages: q rows of [heads dk] at the front of ``q``
-    (row stride free), out [N, heads dv]; see ``csrc/attention_chunk.cu``."""
+    (row stride free), out [N, heads dv]; ``tile_rows``: the rows of a tile that ``items`` were
+    cut for (``chunk_rows_per_tile``); see ``csrc/attention_chunk.cu``."""
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype
           and out.shape[1] == heads * value_dim, "chunk_attention: q, out and pages")
     _i32(block_table, "block_table"), _i32(items, "items")
@@ -209,4 +224,4 @@ def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
                              ctx.seq_qlen.data_ptr(), ctx.seq_pos0.data_ptr(), items.data_ptr(),
                              items.shape[0], r1.data_ptr(), r2.data_ptr(), heads, kv_heads,
                              key_dim, value_dim, k_pages.shape[2], float(scale), int(chunk),
-                             ctx.status.data_ptr(), _stream()), "chunk_attention")
+                             int(tile_rows), ctx.status.data_ptr(), _stream()), "chunk_attention")

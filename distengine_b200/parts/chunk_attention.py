@@ -42,7 +42,7 @@ class ChunkAttention(ProjectedMixer):
                              f"{key_dim} and {value_dim}")
         self.width, self.heads, self.kv_heads = width, heads, kv_heads
         self.dk, self.dv, self.scale, self.chunk, self.eps = key_dim, value_dim, scale, chunk, eps
-        self.key = f"chunk_attention/{heads // kv_heads}/{kv_heads}"
+        self.key = f"chunk_attention/{heads // kv_heads}/{kv_heads}/{key_dim}/{value_dim}"
 
     def tensors(self):
         d, h, g = self.width, self.heads, self.kv_heads
@@ -74,9 +74,13 @@ class ChunkAttention(ProjectedMixer):
         if prep.has(name):
             return
         host = prep.host
+        # tiles of 32 rows when the step brings prompt portions, of 8 for single tokens
+        rows = rk.chunk_rows_per_tile(self.dtype, self.dk, self.dv,
+                                      int(host.seq_qlen.max()) > 1)
         plan = build_plan(host.seq_qlen, host.seq_pos0, self.heads // self.kv_heads,
-                          self.kv_heads, rk.chunk_rows_per_tile(), 0, chunk=0)
+                          self.kv_heads, rows, 0, chunk=0)
         prep.add(name, plan.items)
+        prep.notes[self.key] = rows
 
     def run(self, proj, ctx, cache):
         if cache is None or cache.kind != "paged":
@@ -88,7 +92,8 @@ class ChunkAttention(ProjectedMixer):
         context = ctx.buffer("chunk_attention.context", (n, self.heads * self.dv))
         rk.chunk_attention(proj, context, cache.k_pages, cache.v_pages, cache.block_table,
                            ctx.arrays[self.key + "/items"], self.r1, self.r2, self.heads,
-                           self.kv_heads, self.dk, self.dv, self.scale, self.chunk, ctx)
+                           self.kv_heads, self.dk, self.dv, self.scale, self.chunk, ctx,
+                           tile_rows=ctx.notes[self.key])
         out = ctx.buffer("chunk_attention.out", (n, self.width))
         ops.linear(context, self.w_o, out=out, status=ctx.status)
         return out

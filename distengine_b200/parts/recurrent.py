@@ -164,9 +164,10 @@ class GatedDeltaRule(ProjectedMixer):
         gdec = ctx.buffer("delta.g", (n, H * dk), f32)
         rk.delta_prep(proj, a, self.conv, self.dt_bias, self.a_log, cache.state, self.state_rows,
                       ctx, qn, kn, vv, beta, gdec, H, G, dk, dv, self.b_col)
-        rk.conv_state(proj, cache.state, self.state_rows, self.channels, self.taps, ctx)
         o = ctx.buffer("delta.o", (n, H * dv), f32)
-        rk.state_scan(qn, kn, vv, cache.state, o, H, G, dk, dv, ctx, g=gdec, beta=beta)
+        # (the scan also moves the slot's kept convolution inputs on: the preparation has read them)
+        rk.state_scan(qn, kn, vv, cache.state, o, H, G, dk, dv, ctx, g=gdec, beta=beta,
+                      keep=(proj, self.state_rows, self.channels, self.taps))
         gated = ctx.buffer("delta.gated", (n, H * dv))
         rk.head_gate(o, gate, self.norm, gated, H, dv, self.eps)
         out = ctx.buffer("delta.out", (n, self.width))

@@ -240,7 +240,8 @@ def _plain_chunk_attention(q, k, v, r1, r2, scale, size, pos_q):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,dk,dv,size,page", [(4, 2, 32, 16, 24, 16), (3, 3, 20, 40, 7, 8),
-                                                  (6, 1, 12, 70, 50, 32), (2, 2, 96, 64, 100, 16)])
+                                                  (6, 1, 12, 70, 50, 32), (2, 2, 96, 64, 100, 16),
+                                                  (8, 2, 128, 256, 40, 16), (1, 1, 256, 8, 33, 8)])
 def test_chunk_attention_sees_its_chunk_and_nothing_else(dtype, H, G, dk, dv, size, page):
     """A prompt portion and single tokens over the pages.  The key just before every chunk's start
     is made to match the queries far better than any other (seeing it would take the whole
@@ -261,18 +262,18 @@ def test_chunk_attention_sees_its_chunk_and_nothing_else(dtype, H, G, dk, dv, si
     r1, r2 = torch.rand(H, generator=g) + 0.3, torch.rand(H, generator=g) + 0.1
     scale = 0.4 / dk ** 0.5
     kp, vp, table = _paged(k, v, page, dtype, size)
-    rows = rk.chunk_rows_per_tile()
     # a portion that starts inside a chunk and crosses two edges, then tokens one by one
     first = size - 2
     for lo, n in [(first, size + 5)] + [(p, 1) for p in range(first + size + 5, T)]:
         ctx = _ctx((n,), (lo,), (1,))
+        rows = rk.chunk_rows_per_tile(dtype, dk, dv, n > 1)
         plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H // G, G, rows, 0, chunk=0)
         items = torch.from_numpy(plan.items).to(DEV)
         wide = torch.zeros(n, H * dk + 9, dtype=dtype, device=DEV)
         wide[:, : H * dk] = q[lo: lo + n].reshape(n, -1).to(DEV)
         out = torch.empty(n, H * dv, dtype=dtype, device=DEV)
         rk.chunk_attention(wide, out, kp, vp, table, items, r1.to(DEV), r2.to(DEV), H, G, dk, dv,
-                           scale, size, ctx)
+                           scale, size, ctx, tile_rows=rows)
         assert int(ctx.status.item()) == 0
         want = _plain_chunk_attention(q[lo: lo + n], k, v, r1, r2, scale, size,
                                       list(range(lo, lo + n)))
