@@ -497,13 +497,17 @@ def vomotar_kernels(peak: dict) -> list[dict]:
         items = torch.from_numpy(plan.items).to(dev)
         ao = torch.empty(n, AH * dv, dtype=bf16, device=dev)
         r = torch.rand(AH, device=dev)
-        us = timed(lambda: rk.chunk_attention(aproj, ao, kp, vp, table, items, r, r, AH, G, dk, dv,
-                                              0.09, chunk, ctx, tile_rows=rows))
+        if n == s and rk.chunk_decode_ok(bf16, AH, G, dk, dv):      # as the mixer chooses
+            us = timed(lambda: rk.chunk_attention_decode(aproj, ao, kp, vp, table, r, r, AH, G, dk,
+                                                         dv, 0.09, chunk, ctx))
+        else:
+            us = timed(lambda: rk.chunk_attention(aproj, ao, kp, vp, table, items, r, r, AH, G, dk,
+                                                  dv, 0.09, chunk, ctx, tile_rows=rows))
         keys = sum(sum(min(p + i, (p + i) % chunk) + 1 for i in range(l))
                    for p, l in zip(pos0, lens))
         record("chunk_attention", case, us,
                bytes_=sum(min(p + l, chunk + l) for p, l in zip(pos0, lens)) * G * (dk + dv) * 2,
-               flops=keys * AH * (dk + dv))
+               flops=2 * keys * AH * (dk + dv))
         x1 = torch.randn(n, width, device=dev).to(bf16)
         x2 = torch.randn(n, width, device=dev).to(bf16)
         w32 = torch.rand(width, device=dev)

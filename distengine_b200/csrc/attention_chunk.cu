@@ -408,6 +408,172 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
     }
 }
 
+
+// ------------------------------------------------------------------------------------------
+// Steps in which every sequence brings one token.  A block takes a sequence and a kv head; its
+// eight warps share the key tiles of the token's chunk out among themselves (warp w takes tiles
+// w, w + 8, ...) and each works alone: a lane reads its key's row straight from the page in
+// 16-byte pieces, the values come row by row as the weights are handed round, nothing goes through
+// shared memory but the queries.  All RW query heads of the group ride on every key read.  The
+// warps' partial results (maximum, sum, weighted values) are merged in ascending order of the
+// warps.  Sizes as the kernel above; RW >= heads / kv_heads.
+// ------------------------------------------------------------------------------------------
+template <typename T, int RW>
+__global__ void __launch_bounds__(ROWS * 32)
+attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
+                         int out_stride, const T* __restrict__ k_pages,
+                         const T* __restrict__ v_pages, const int* __restrict__ block_table,
+                         int table_stride, int num_pages, const int* __restrict__ seq_slot,
+                         const int* __restrict__ seq_qstart, const int* __restrict__ seq_pos0,
+                         const float* __restrict__ r1, const float* __restrict__ r2, int heads,
+                         int kv_heads, int dk, int dv, int page, float scale, int chunk,
+                         int* __restrict__ status) {
+    constexpr int PN = Piece<T>::N;
+    extern __shared__ __align__(16) float smem[];
+    float* Qs = smem;                                // [RW][dk]
+    float* Pml = Qs + RW * dk;                       // [ROWS warps][RW][2]
+    float* Pacc = Pml + ROWS * RW * 2;               // [ROWS warps][RW][dv]
+    const int seq = blockIdx.x, hk = blockIdx.y;
+    const int g = heads / kv_heads;
+    const int pos = seq_pos0[seq], slot = seq_slot[seq], tok = seq_qstart[seq];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int lo = chunk > 0 ? pos / chunk * chunk : 0, hi = pos + 1;
+    float pen1[RW], pen2[RW], m[RW], l[RW];
+#pragma unroll
+    for (int i = 0; i < RW; ++i) {
+        const int hq = hk * g + min(i, g - 1);
+        pen1[i] = r1[hq];
+        pen2[i] = r2[hq];
+        m[i] = -INFINITY;
+        l[i] = 0.0f;
+    }
+    pdl_wait();
+    for (int e = threadIdx.x; e < RW * dk; e += ROWS * 32) {
+        const int i = e / dk, d = e - i * dk;
+        Qs[e] = i < g ? to_float(q[(size_t)tok * q_stride + (hk * g + i) * dk + d]) : 0.0f;
+    }
+    __syncthreads();
+    float acc[RW][MAX_D / 32];
+#pragma unroll
+    for (int i = 0; i < RW; ++i)
+#pragma unroll
+        for (int b = 0; b < MAX_D / 32; ++b) acc[i][b] = 0.0f;
+
+    for (int kt = (lo / TILE) * TILE + warp * TILE; kt < hi; kt += ROWS * TILE) {
+        const int kpos = kt + lane;
+        bool valid = kpos >= lo && kpos < hi;
+        size_t row = 0;
+        if (valid) {
+            const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
+            if (page_id < 0 || page_id >= num_pages) {
+                valid = false;
+                if (status != nullptr) atomicExch(status, 2);
+            } else {
+                row = ((size_t)page_id * kv_heads + hk) * page + (size_t)(kpos % page);
+            }
+        }
+        float s[RW];
+#pragma unroll
+        for (int i = 0; i < RW; ++i) s[i] = 0.0f;
+        const uint4* kp = reinterpret_cast<const uint4*>(k_pages + row * dk);
+#pragma unroll 4
+        for (int piece = 0; piece < dk / PN; ++piece) {
+            float f[PN];
+            Piece<T>::unpack(valid ? kp[piece] : make_uint4(0u, 0u, 0u, 0u), f);
+#pragma unroll
+            for (int i = 0; i < RW; ++i) {
+                const float4* q4 = reinterpret_cast<const float4*>(Qs + i * dk + piece * PN);
+#pragma unroll
+                for (int x = 0; x < PN / 4; ++x) {
+                    const float4 qq = q4[x];
+                    s[i] = fmaf(qq.x, f[4 * x + 0], s[i]);
+                    s[i] = fmaf(qq.y, f[4 * x + 1], s[i]);
+                    s[i] = fmaf(qq.z, f[4 * x + 2], s[i]);
+                    s[i] = fmaf(qq.w, f[4 * x + 3], s[i]);
+                }
+            }
+        }
+        float p[RW];
+        const float dist = (float)(pos - kpos);
+#pragma unroll
+        for (int i = 0; i < RW; ++i) {
+            const float sc = valid ? s[i] * scale - pen1[i] * log1pf(pen2[i] * dist) : -INFINITY;
+            const float m_new = fmaxf(m[i], warp_max(sc));
+            if (m_new == -INFINITY) {
+                p[i] = 0.0f;
+                continue;
+            }
+            p[i] = valid ? expf(sc - m_new) : 0.0f;
+            const float corr = expf(m[i] - m_new);
+            l[i] = l[i] * corr + warp_sum(p[i]);
+#pragma unroll
+            for (int b = 0; b < MAX_D / 32; ++b) acc[i][b] *= corr;
+            m[i] = m_new;
+        }
+#pragma unroll 4
+        for (int j = 0; j < TILE; ++j) {
+            const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)row, j);
+            float pj[RW];
+            bool zero = true;
+#pragma unroll
+            for (int i = 0; i < RW; ++i) {
+                pj[i] = __shfl_sync(0xffffffffu, p[i], j);
+                zero &= pj[i] == 0.0f;
+            }
+            if (zero) continue;
+            const T* vr = v_pages + (size_t)rj * dv;
+#pragma unroll
+            for (int b = 0; b < MAX_D / 32; ++b) {
+                const int dd = lane + 32 * b;
+                if (dd < dv) {
+                    const float vv = to_float(vr[dd]);
+#pragma unroll
+                    for (int i = 0; i < RW; ++i) acc[i][b] = fmaf(pj[i], vv, acc[i][b]);
+                }
+            }
+        }
+    }
+    pdl_trigger();
+#pragma unroll
+    for (int i = 0; i < RW; ++i) {
+        if (lane == 0) {
+            Pml[(warp * RW + i) * 2] = m[i];
+            Pml[(warp * RW + i) * 2 + 1] = l[i];
+        }
+#pragma unroll
+        for (int b = 0; b < MAX_D / 32; ++b) {
+            const int dd = lane + 32 * b;
+            if (dd < dv) Pacc[(size_t)(warp * RW + i) * dv + dd] = acc[i][b];
+        }
+    }
+    __syncthreads();
+    for (int i = warp; i < g; i += ROWS) {
+        float top = -INFINITY;
+        for (int w = 0; w < ROWS; ++w) top = fmaxf(top, Pml[(w * RW + i) * 2]);
+        float sum = 0.0f, res[MAX_D / 32];
+#pragma unroll
+        for (int b = 0; b < MAX_D / 32; ++b) res[b] = 0.0f;
+        for (int w = 0; w < ROWS; ++w) {
+            const float mw = Pml[(w * RW + i) * 2];
+            if (mw == -INFINITY) continue;
+            const float f = expf(mw - top);
+            sum = fmaf(Pml[(w * RW + i) * 2 + 1], f, sum);
+#pragma unroll
+            for (int b = 0; b < MAX_D / 32; ++b) {
+                const int dd = lane + 32 * b;
+                if (dd < dv) res[b] = fmaf(Pacc[(size_t)(w * RW + i) * dv + dd], f, res[b]);
+            }
+        }
+        const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+        T* o = out + (size_t)tok * out_stride + (hk * g + i) * dv;
+#pragma unroll
+        for (int b = 0; b < MAX_D / 32; ++b) {
+            const int dd = lane + 32 * b;
+            if (dd < dv) o[dd] = from_float<T>(res[b] * inv);
+        }
+    }
+}
+
 }  // namespace
 
 // rows of a tile: 8, or 32 when the step brings prompt portions (`wide`) and the sizes allow the
@@ -418,6 +584,53 @@ static bool vec_ok(int dtype, int dk, int dv) {
 }
 DE_EXPORT int de_attn_chunk_rows(int dtype, int dk, int dv, int wide) {
     return vec_ok(dtype, dk, dv) && wide ? ROWS * 4 : ROWS;
+}
+
+// Whether steps of single tokens go to the kernel that takes a (sequence, kv head) a block.
+DE_EXPORT int de_attn_chunk_decode_ok(int dtype, int heads, int kv_heads, int dk, int dv) {
+    return vec_ok(dtype, dk, dv) && kv_heads > 0 && heads % kv_heads == 0 && heads / kv_heads <= 8;
+}
+
+DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void* out,
+                                   int out_stride, const void* k_pages, const void* v_pages,
+                                   const int* block_table, int table_stride, int num_pages,
+                                   const int* seq_slot, const int* seq_qstart,
+                                   const int* seq_pos0, int n_seqs, const float* r1,
+                                   const float* r2, int heads, int kv_heads, int dk, int dv,
+                                   int page, float scale, int chunk, int* status, void* stream) {
+    if (n_seqs <= 0) return 0;
+    if (!de_attn_chunk_decode_ok(dtype, heads, kv_heads, dk, dv) || (uintptr_t)k_pages % 16 != 0)
+        return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int g = heads / kv_heads;
+    const int rw = g <= 1 ? 1 : (g <= 2 ? 2 : (g <= 4 ? 4 : 8));
+    const size_t smem = (size_t)(rw * dk + ROWS * rw * 2 + ROWS * rw * dv) * sizeof(float);
+    dim3 grid(n_seqs, kv_heads);
+#define DEC(T, RW)                                                                              \
+    do {                                                                                        \
+        if (smem > 48 * 1024) {                                                                 \
+            cudaError_t e = cudaFuncSetAttribute(attn_chunk_decode_kernel<T, RW>,               \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                                 (int)smem);                                    \
+            if (e != cudaSuccess) return (int)e;                                                \
+        }                                                                                       \
+        return de_launch(attn_chunk_decode_kernel<T, RW>, grid, dim3(ROWS * 32), smem, s,       \
+                         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages,         \
+                         (const T*)v_pages, block_table, table_stride, num_pages, seq_slot,     \
+                         seq_qstart, seq_pos0, r1, r2, heads, kv_heads, dk, dv, page, scale,    \
+                         chunk, status);                                                        \
+    } while (0)
+#define DEC_T(T)                                                                                \
+    do {                                                                                        \
+        if (rw == 1) DEC(T, 1);                                                                 \
+        if (rw == 2) DEC(T, 2);                                                                 \
+        if (rw == 4) DEC(T, 4);                                                                 \
+        DEC(T, 8);                                                                              \
+    } while (0)
+    if (dtype == DE_BF16) DEC_T(__nv_bfloat16);
+    DEC_T(float);
+#undef DEC_T
+#undef DEC
 }
 
 DE_EXPORT int de_kv_write_normed(int dtype, const void* proj, int ld, int k_col,

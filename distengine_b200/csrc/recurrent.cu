@@ -9,8 +9,8 @@
 //
 // The columns of S never meet: column j needs k_t, q_t, g_t, beta_t and v_t[j] only.  The scan
 // kernel therefore gives a column to four adjacent lanes (each holds a quarter of its rows in
-// registers), so a token costs two short chains of multiply-adds and two butterfly sums over four
-// lanes, and a block of 32 columns walks its sequence's tokens of the step one after the other
+// registers), so a token costs short chains of multiply-adds and butterfly sums over four lanes,
+// and a block of up to 32 columns walks its sequence's tokens of the step one after the other
 // while the next tokens' vectors arrive through cp.async.  The order of every sum depends on the
 // head's sizes only: a state does not depend, bit for bit, on how its tokens were cut into steps.
 //
@@ -292,45 +292,55 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
             if (t >= count) break;
             const float4* q4 = reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD);
             const float4* k4 = reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD + PD);
+            // The read-out needs no second pass over the new state: with D = diag(g) S,
+            //   S' = D + k u^T  and  o = S'^T q = D^T q + u (k . q),
+            // so D^T k, D^T q and k . q are summed together (three sums over the quarter's rows,
+            // one butterfly over the four quarters for all three) and the update of S is the
+            // last thing a token does, off the next token's critical path but for S itself.
             float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+            float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;      // k . q
+            float u;
             if (DELTA) {
                 const float4* g4 =
                     reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD + 2 * PD);
                 float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
 #pragma unroll
                 for (int r = 0; r < R / 4; ++r) {
-                    const float4 gg = g4[r], kk = k4[r];
-                    S[4 * r + 0] *= gg.x; p0 = fmaf(S[4 * r + 0], kk.x, p0);
-                    S[4 * r + 1] *= gg.y; p1 = fmaf(S[4 * r + 1], kk.y, p1);
-                    S[4 * r + 2] *= gg.z; p2 = fmaf(S[4 * r + 2], kk.z, p2);
-                    S[4 * r + 3] *= gg.w; p3 = fmaf(S[4 * r + 3], kk.w, p3);
+                    const float4 gg = g4[r], kk = k4[r], qq = q4[r];
+                    S[4 * r + 0] *= gg.x; p0 = fmaf(S[4 * r + 0], kk.x, p0); o0 = fmaf(S[4 * r + 0], qq.x, o0); c0 = fmaf(kk.x, qq.x, c0);
+                    S[4 * r + 1] *= gg.y; p1 = fmaf(S[4 * r + 1], kk.y, p1); o1 = fmaf(S[4 * r + 1], qq.y, o1); c1 = fmaf(kk.y, qq.y, c1);
+                    S[4 * r + 2] *= gg.z; p2 = fmaf(S[4 * r + 2], kk.z, p2); o2 = fmaf(S[4 * r + 2], qq.z, o2); c2 = fmaf(kk.z, qq.z, c2);
+                    S[4 * r + 3] *= gg.w; p3 = fmaf(S[4 * r + 3], kk.w, p3); o3 = fmaf(S[4 * r + 3], qq.w, o3); c3 = fmaf(kk.w, qq.w, c3);
                 }
                 float part = (p0 + p1) + (p2 + p3);
                 part += __shfl_xor_sync(0xffffffffu, part, 1);
                 part += __shfl_xor_sync(0xffffffffu, part, 2);
-                const float u = bt[t] * (vt[t] - part);
-#pragma unroll
-                for (int r = 0; r < R / 4; ++r) {
-                    const float4 kk = k4[r], qq = q4[r];
-                    S[4 * r + 0] = fmaf(kk.x, u, S[4 * r + 0]); o0 = fmaf(S[4 * r + 0], qq.x, o0);
-                    S[4 * r + 1] = fmaf(kk.y, u, S[4 * r + 1]); o1 = fmaf(S[4 * r + 1], qq.y, o1);
-                    S[4 * r + 2] = fmaf(kk.z, u, S[4 * r + 2]); o2 = fmaf(S[4 * r + 2], qq.z, o2);
-                    S[4 * r + 3] = fmaf(kk.w, u, S[4 * r + 3]); o3 = fmaf(S[4 * r + 3], qq.w, o3);
-                }
+                u = bt[t] * (vt[t] - part);
             } else {
-                const float u = vt[t];
+                u = vt[t];
 #pragma unroll
                 for (int r = 0; r < R / 4; ++r) {
                     const float4 kk = k4[r], qq = q4[r];
-                    S[4 * r + 0] = fmaf(kk.x, u, S[4 * r + 0] * dec); o0 = fmaf(S[4 * r + 0], qq.x, o0);
-                    S[4 * r + 1] = fmaf(kk.y, u, S[4 * r + 1] * dec); o1 = fmaf(S[4 * r + 1], qq.y, o1);
-                    S[4 * r + 2] = fmaf(kk.z, u, S[4 * r + 2] * dec); o2 = fmaf(S[4 * r + 2], qq.z, o2);
-                    S[4 * r + 3] = fmaf(kk.w, u, S[4 * r + 3] * dec); o3 = fmaf(S[4 * r + 3], qq.w, o3);
+                    S[4 * r + 0] *= dec; o0 = fmaf(S[4 * r + 0], qq.x, o0); c0 = fmaf(kk.x, qq.x, c0);
+                    S[4 * r + 1] *= dec; o1 = fmaf(S[4 * r + 1], qq.y, o1); c1 = fmaf(kk.y, qq.y, c1);
+                    S[4 * r + 2] *= dec; o2 = fmaf(S[4 * r + 2], qq.z, o2); c2 = fmaf(kk.z, qq.z, c2);
+                    S[4 * r + 3] *= dec; o3 = fmaf(S[4 * r + 3], qq.w, o3); c3 = fmaf(kk.w, qq.w, c3);
                 }
             }
-            float o = (o0 + o1) + (o2 + o3);
+            float o = (o0 + o1) + (o2 + o3), kq = (c0 + c1) + (c2 + c3);
             o += __shfl_xor_sync(0xffffffffu, o, 1);
+            kq += __shfl_xor_sync(0xffffffffu, kq, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);
+            kq += __shfl_xor_sync(0xffffffffu, kq, 2);
+            o = fmaf(u, kq, o);
+#pragma unroll
+            for (int r = 0; r < R / 4; ++r) {
+                const float4 kk = k4[r];
+                S[4 * r + 0] = fmaf(kk.x, u, S[4 * r + 0]);
+                S[4 * r + 1] = fmaf(kk.y, u, S[4 * r + 1]);
+                S[4 * r + 2] = fmaf(kk.z, u, S[4 * r + 2]);
+                S[4 * r + 3] = fmaf(kk.w, u, S[4 * r + 3]);
+            }
             if (live && l == 0)
                 out[(size_t)(tok0 + b * TB + t) * (H * dv) + h * dv + col] = o;
         }

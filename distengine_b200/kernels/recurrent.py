@@ -182,6 +182,37 @@ def chunk_rows_per_tile(dtype: torch.dtype, key_dim: int, value_dim: int, wide: 
                                                                   int(wide)))
 
 
+def chunk_decode_ok(dtype: torch.dtype, heads: int, kv_heads: int, key_dim: int,
+                    value_dim: int) -> bool:
+    """Whether steps of single tokens can go to ``chunk_attention_decode``."""
+    return bool(library.load("attention_chunk").de_attn_chunk_decode_ok(
+        _tag(dtype), heads, kv_heads, key_dim, value_dim))
+
+
+def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
+                           v_pages: torch.Tensor, block_table: torch.Tensor, r1: torch.Tensor,
+                           r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
+                           value_dim: int, scale: float, chunk: int, ctx) -> None:
+    """``chunk_attention`` for a step in which every sequence brings one token: a block a
+    (sequence, kv head), its warps share the key tiles out; no work items."""
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype
+          and out.shape[1] == heads * value_dim and q.shape[0] == ctx.n_seqs,
+          "chunk_attention_decode: q, out and pages; one token a sequence")
+    _i32(block_table, "block_table")
+    _f32(r1, "r1"), _f32(r2, "r2")
+    _need(r1.shape == r2.shape == (heads,), "chunk_attention_decode: r1, r2 [heads]")
+    lib = library.load("attention_chunk")
+    _check(lib.de_attn_chunk_decode(_tag(q.dtype), q.data_ptr(), q.stride(0), out.data_ptr(),
+                                    out.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
+                                    block_table.data_ptr(), block_table.stride(0),
+                                    k_pages.shape[0], ctx.seq_slot.data_ptr(),
+                                    ctx.seq_qstart.data_ptr(), ctx.seq_pos0.data_ptr(),
+                                    ctx.n_seqs, r1.data_ptr(), r2.data_ptr(), heads, kv_heads,
+                                    key_dim, value_dim, k_pages.shape[2], float(scale),
+                                    int(chunk), ctx.status.data_ptr(), _stream()),
+           "chunk_attention_decode")
+
+
 def kv_write_normed(proj: torch.Tensor, k_col: int, kv_heads: int, key_dim: int, value_dim: int,
                     eps: float, k_pages: torch.Tensor, v_pages: torch.Tensor,
                     block_table: torch.Tensor, ctx) -> None:

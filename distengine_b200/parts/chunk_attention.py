@@ -74,6 +74,12 @@ class ChunkAttention(ProjectedMixer):
         if prep.has(name):
             return
         host = prep.host
+        if int(host.seq_qlen.max()) == 1 and rk.chunk_decode_ok(self.dtype, self.heads,
+                                                               self.kv_heads, self.dk, self.dv):
+            # single tokens only: the kernel that takes a (sequence, kv head) a block, no items
+            prep.add(name, np.zeros((0, 8), dtype=np.int32))
+            prep.notes[self.key] = 0
+            return
         # tiles of 32 rows when the step brings prompt portions, of 8 for single tokens
         rows = rk.chunk_rows_per_tile(self.dtype, self.dk, self.dv,
                                       int(host.seq_qlen.max()) > 1)
@@ -90,10 +96,15 @@ class ChunkAttention(ProjectedMixer):
             rk.kv_write_normed(proj, self.heads * self.dk, self.kv_heads, self.dk, self.dv,
                                self.eps, cache.k_pages, cache.v_pages, cache.block_table, ctx)
         context = ctx.buffer("chunk_attention.context", (n, self.heads * self.dv))
-        rk.chunk_attention(proj, context, cache.k_pages, cache.v_pages, cache.block_table,
-                           ctx.arrays[self.key + "/items"], self.r1, self.r2, self.heads,
-                           self.kv_heads, self.dk, self.dv, self.scale, self.chunk, ctx,
-                           tile_rows=ctx.notes[self.key])
+        if ctx.notes[self.key] == 0:
+            rk.chunk_attention_decode(proj, context, cache.k_pages, cache.v_pages,
+                                      cache.block_table, self.r1, self.r2, self.heads,
+                                      self.kv_heads, self.dk, self.dv, self.scale, self.chunk, ctx)
+        else:
+            rk.chunk_attention(proj, context, cache.k_pages, cache.v_pages, cache.block_table,
+                               ctx.arrays[self.key + "/items"], self.r1, self.r2, self.heads,
+                               self.kv_heads, self.dk, self.dv, self.scale, self.chunk, ctx,
+                               tile_rows=ctx.notes[self.key])
         out = ctx.buffer("chunk_attention.out", (n, self.width))
         ops.linear(context, self.w_o, out=out, status=ctx.status)
         return out

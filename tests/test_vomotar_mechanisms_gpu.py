@@ -278,6 +278,12 @@ def test_chunk_attention_sees_its_chunk_and_nothing_else(dtype, H, G, dk, dv, si
         want = _plain_chunk_attention(q[lo: lo + n], k, v, r1, r2, scale, size,
                                       list(range(lo, lo + n)))
         assert_close(out.view(n, H, dv), want, dtype, f"chunk attention at {lo}+{n}")
+        if n == 1 and rk.chunk_decode_ok(dtype, H, G, dk, dv):      # the single-token kernel
+            out.fill_(float("nan"))
+            rk.chunk_attention_decode(wide, out, kp, vp, table, r1.to(DEV), r2.to(DEV), H, G, dk,
+                                      dv, scale, size, ctx)
+            assert int(ctx.status.item()) == 0
+            assert_close(out.view(n, H, dv), want, dtype, f"single-token kernel at {lo}")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
