@@ -412,12 +412,18 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 // ------------------------------------------------------------------------------------------
 // Steps in which every sequence brings one token.  A block takes a sequence and a kv head; its
 // eight warps share the key tiles of the token's chunk out among themselves (warp w takes tiles
-// w, w + 8, ...) and each works alone: a lane reads its key's row straight from the page in
-// 16-byte pieces, the values come row by row as the weights are handed round, nothing goes through
-// shared memory but the queries.  All RW query heads of the group ride on every key read.  The
+// w, w + 8, ...) and each works alone: it asks for its tile's 32 key rows and 32 value rows at
+// once (cp.async, 16 bytes a piece, into shared memory of its own), so a tile costs one trip to
+// memory; then a lane takes its key's row, and the values come row by row as the weights are
+// handed round.  All RW query heads of the group ride on every key read.  The
 // warps' partial results (maximum, sum, weighted values) are merged in ascending order of the
 // warps.  Sizes as the kernel above; RW >= heads / kv_heads.
 // ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src) : "memory");
+}
+
 template <typename T, int RW>
 __global__ void __launch_bounds__(ROWS * 32)
 attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
@@ -433,6 +439,13 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     float* Qs = smem;                                // [RW][dk]
     float* Pml = Qs + RW * dk;                       // [ROWS warps][RW][2]
     float* Pacc = Pml + ROWS * RW * 2;               // [ROWS warps][RW][dv]
+    // a warp's tile: key rows at a stride that keeps 16-byte reads of 8 lanes on different banks
+    const int k_stride = ((dk * (int)sizeof(T) + 127) / 128) * 128 + 16;       // bytes
+    const int tile_bytes = TILE * k_stride + TILE * dv * (int)sizeof(T);
+    char* mine = reinterpret_cast<char*>(Pacc + ROWS * RW * dv) +
+                 (size_t)(threadIdx.x >> 5) * tile_bytes;
+    char* Kt = mine;
+    const T* Vt = reinterpret_cast<const T*>(mine + TILE * k_stride);
     const int seq = blockIdx.x, hk = blockIdx.y;
     const int g = heads / kv_heads;
     const int pos = seq_pos0[seq], slot = seq_slot[seq], tok = seq_qstart[seq];
@@ -472,10 +485,31 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 row = ((size_t)page_id * kv_heads + hk) * page + (size_t)(kpos % page);
             }
         }
+        __syncwarp();                                // the tile before this one has been used
+        {
+            const int ck = dk / PN, cv = dv / PN;
+            for (int e = lane; e < TILE * ck; e += 32) {
+                const int j = e / ck, w = e - j * ck;
+                const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)row, j);
+                const bool ok = __shfl_sync(0xffffffffu, (int)valid, j) != 0;
+                if (ok) cp_async_16(Kt + j * k_stride + w * 16, k_pages + (size_t)rj * dk + w * PN);
+            }
+            for (int e = lane; e < TILE * cv; e += 32) {
+                const int j = e / cv, w = e - j * cv;
+                const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)row, j);
+                const bool ok = __shfl_sync(0xffffffffu, (int)valid, j) != 0;
+                if (ok)
+                    cp_async_16(mine + TILE * k_stride + ((size_t)j * dv + w * PN) * sizeof(T),
+                                v_pages + (size_t)rj * dv + w * PN);
+            }
+            asm volatile("cp.async.commit_group;\n" ::: "memory");
+            asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+            __syncwarp();
+        }
         float s[RW];
 #pragma unroll
         for (int i = 0; i < RW; ++i) s[i] = 0.0f;
-        const uint4* kp = reinterpret_cast<const uint4*>(k_pages + row * dk);
+        const uint4* kp = reinterpret_cast<const uint4*>(Kt + lane * k_stride);
 #pragma unroll 4
         for (int piece = 0; piece < dk / PN; ++piece) {
             float f[PN];
@@ -512,7 +546,6 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         }
 #pragma unroll 4
         for (int j = 0; j < TILE; ++j) {
-            const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)row, j);
             float pj[RW];
             bool zero = true;
 #pragma unroll
@@ -521,7 +554,7 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                 zero &= pj[i] == 0.0f;
             }
             if (zero) continue;
-            const T* vr = v_pages + (size_t)rj * dv;
+            const T* vr = Vt + (size_t)j * dv;
 #pragma unroll
             for (int b = 0; b < MAX_D / 32; ++b) {
                 const int dd = lane + 32 * b;
@@ -586,9 +619,20 @@ DE_EXPORT int de_attn_chunk_rows(int dtype, int dk, int dv, int wide) {
     return vec_ok(dtype, dk, dv) && wide ? ROWS * 4 : ROWS;
 }
 
-// Whether steps of single tokens go to the kernel that takes a (sequence, kv head) a block.
+static size_t decode_smem(int dtype, int rw, int dk, int dv) {
+    const int size = dtype == DE_BF16 ? 2 : 4;
+    const size_t tile = (size_t)TILE * (((dk * size + 127) / 128) * 128 + 16) + (size_t)TILE * dv * size;
+    return (size_t)(rw * dk + ROWS * rw * 2 + ROWS * rw * dv) * sizeof(float) + ROWS * tile;
+}
+
+// Whether steps of single tokens go to the kernel that takes a (sequence, kv head) a block: rows
+// of whole 16-byte pieces, at most 8 query heads a kv head, and its eight tiles fit an SM.
 DE_EXPORT int de_attn_chunk_decode_ok(int dtype, int heads, int kv_heads, int dk, int dv) {
-    return vec_ok(dtype, dk, dv) && kv_heads > 0 && heads % kv_heads == 0 && heads / kv_heads <= 8;
+    if (!(vec_ok(dtype, dk, dv) && kv_heads > 0 && heads % kv_heads == 0 && heads / kv_heads <= 8))
+        return 0;
+    const int g = heads / kv_heads;
+    const int rw = g <= 1 ? 1 : (g <= 2 ? 2 : (g <= 4 ? 4 : 8));
+    return decode_smem(dtype, rw, dk, dv) <= 200 * 1024;
 }
 
 DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void* out,
@@ -604,7 +648,8 @@ DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void*
     cudaStream_t s = (cudaStream_t)stream;
     const int g = heads / kv_heads;
     const int rw = g <= 1 ? 1 : (g <= 2 ? 2 : (g <= 4 ? 4 : 8));
-    const size_t smem = (size_t)(rw * dk + ROWS * rw * 2 + ROWS * rw * dv) * sizeof(float);
+    const size_t smem = decode_smem(dtype, rw, dk, dv);
+    if ((uintptr_t)v_pages % 16 != 0) return -2;
     dim3 grid(n_seqs, kv_heads);
 #define DEC(T, RW)                                                                              \
     do {                                                                                        \
