@@ -59,8 +59,10 @@ __global__ void delta_prep_kernel(const T* __restrict__ proj, int ld, const floa
     const int off = positions[n] - seq_pos0[seq];   // the token's place in its sequence's portion
     pdl_wait();
     const float* cs = state + (size_t)slot * slot_stride + conv_offset;
+#pragma unroll 2
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
         float acc = 0.0f;
+#pragma unroll 4
         for (int j = 0; j < K; ++j) {
             const int rel = off - (K - 1) + j;
             const float x = rel >= 0 ? to_float(proj[(size_t)(n - (K - 1) + j) * ld + c])
@@ -156,8 +158,9 @@ __global__ void retention_prep_kernel(const T* __restrict__ proj, int ld,
 // (quarter l at l * (R + 4)), so four consecutive rows are 16 bytes there as in memory (one
 // cp.async), a quarter reads its share as float4 and the four quarters of a warp hit different
 // banks.  COLS is 32, or less when a step has so few (sequence, head) pairs that blocks of 32
-// columns would leave most SMs idle.  Block (s, 0, 0) also moves the slot's kept convolution
-// inputs on (`conv_*`; the kernel before this one has read the old ones).
+// columns would leave most SMs idle.  A sequence's blocks also move the slot's kept convolution
+// inputs on, a share of the channels each (`conv_*`; the kernel before this one has read the old
+// ones).
 // ------------------------------------------------------------------------------------------
 constexpr int TB = 8;          // tokens whose vectors are in flight together
 
@@ -205,9 +208,10 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
     pdl_wait();
 
     float* slot_state = state + (size_t)seq_slot[s] * slot_stride;
-    if (keep.K > 1 && h == 0 && blockIdx.z == 0) {
+    if (keep.K > 1) {                                // the sequence's blocks share the channels out
         float* cs = slot_state + keep.offset;
-        for (int c = threadIdx.x; c < keep.C; c += COLS * 4)
+        const int rank = h * gridDim.z + blockIdx.z, blocks = H * gridDim.z;
+        for (int c = rank * (COLS * 4) + threadIdx.x; c < keep.C; c += blocks * (COLS * 4))
             for (int i = 0; i < keep.K - 1; ++i) {   // ascending: what is read lies ahead
                 const int rel = qlen - (keep.K - 1) + i;
                 float x;
@@ -493,8 +497,12 @@ DE_EXPORT int de_delta_prep(int dtype, const void* proj, int ld, const float* a,
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)2 * G * dk * sizeof(float);
     if (smem > 48 * 1024) return -3;
+    // a block a token: many threads, so that a token of a decode step is a few rounds of loads
+    // (with few tokens: steps of many tokens fill the GPU with blocks of 256)
+    const int work = 2 * G * dk + H * dv;
+    const int threads = n >= 512 ? 256 : (work >= 4096 ? 1024 : (work >= 1024 ? 512 : 256));
 #define PREP(T)                                                                                 \
-    return de_launch(delta_prep_kernel<T>, dim3(n), dim3(256), smem, s, (const T*)proj, ld, a,  \
+    return de_launch(delta_prep_kernel<T>, dim3(n), dim3(threads), smem, s, (const T*)proj, ld, a,  \
                      taps, dt_bias, a_log, state, slot_stride, conv_offset, token_seq,          \
                      token_slot, positions, seq_pos0, qn, kn, vv, beta, gdec, H, G, dk, dv, K,  \
                      b_col)
@@ -523,11 +531,12 @@ DE_EXPORT int de_retention_prep(int dtype, const void* proj, int ld, const int* 
     if (n <= 0) return 0;
     if (rot < 0 || rot % 2 || rot > dk) return -2;
     cudaStream_t s = (cudaStream_t)stream;
+    const int threads = n >= 512 ? 256 : (2 * H * dk >= 2048 ? 1024 : (2 * H * dk >= 512 ? 512 : 256));
     if (dtype == DE_BF16)
-        return de_launch(retention_prep_kernel<__nv_bfloat16>, dim3(n), dim3(256), 0, s,
+        return de_launch(retention_prep_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s,
                          (const __nv_bfloat16*)proj, ld, positions, inv_freq, rot, H, dk, qr, kr);
-    return de_launch(retention_prep_kernel<float>, dim3(n), dim3(256), 0, s, (const float*)proj,
-                     ld, positions, inv_freq, rot, H, dk, qr, kr);
+    return de_launch(retention_prep_kernel<float>, dim3(n), dim3(threads), 0, s,
+                     (const float*)proj, ld, positions, inv_freq, rot, H, dk, qr, kr);
 }
 
 // v_dtype: the type of v (DE_F32 for the delta rule, whose values come from its own preparation).
