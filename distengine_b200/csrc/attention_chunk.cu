@@ -206,7 +206,7 @@ template <> struct Piece<__nv_bfloat16> {
 };
 
 template <typename T, int RW, int NCH>
-__global__ void __launch_bounds__(ROWS * 32)
+__global__ void __launch_bounds__(ROWS * 32, NCH <= 4 ? 2 : 1)
 attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                       const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                       const int* __restrict__ block_table, int table_stride, int num_pages,
@@ -330,6 +330,7 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
         float s[RW];
 #pragma unroll
         for (int i = 0; i < RW; ++i) s[i] = 0.0f;
+#pragma unroll 4
         for (int d = 0; d < dk / 4; ++d) {
             const float4 kk = kr[d];
 #pragma unroll
@@ -365,6 +366,7 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
             some = true;
         }
         if (!some) continue;
+#pragma unroll 4
         for (int j = 0; j < TILE; ++j) {
             float pj[RW];
             bool zero = true;

@@ -152,12 +152,12 @@ __global__ void retention_prep_kernel(const T* __restrict__ proj, int ld,
 }
 
 // ------------------------------------------------------------------------------------------
-// The scan.  grid (sequences, heads, column blocks of COLS); thread = 4 * column + quarter.
-// Rows of the state go to the quarters four at a time: row i belongs to quarter (i / 4) % 4,
-// register 4 * (i / 16) + i % 4; in shared memory a token's vector lies quarter by quarter
-// (quarter l at l * (R + 4)), so four consecutive rows are 16 bytes there as in memory (one
-// cp.async), a quarter reads its share as float4 and the four quarters of a warp hit different
-// banks.  COLS is 32, or less when a step has so few (sequence, head) pairs that blocks of 32
+// The scan.  grid (sequences, heads, column blocks of COLS); a column belongs to LANES = 4
+// adjacent lanes; thread = LANES * column + share.
+// Rows of the state go to the shares four at a time: row i belongs to share (i / 4) % LANES,
+// register 4 * (i / (4 LANES)) + i % 4; in shared memory a token's vector lies share by share
+// (share l at l * (R + 4)), so four consecutive rows are 16 bytes there as in memory (one
+// cp.async), a share reads its rows as float4 and the shares of a warp hit different banks.  COLS is 32, or less when a step has so few (sequence, head) pairs that blocks of 32
 // columns would leave most SMs idle.  A sequence's blocks also move the slot's kept convolution
 // inputs on, a share of the channels each (`conv_*`; the kernel before this one has read the old
 // ones).
@@ -182,12 +182,13 @@ struct ConvKeep {              // the convolution inputs a slot keeps (K <= 1: n
     int ld, bf16, offset, C, K;
 };
 
-__device__ __forceinline__ int state_row(int r, int l) {      // register r of quarter l -> row
-    return ((r >> 2) << 4) + (l << 2) + (r & 3);
+template <int LANES>
+__device__ __forceinline__ int state_row(int r, int l) {      // register r of share l -> row
+    return (r >> 2) * (4 * LANES) + (l << 2) + (r & 3);
 }
 
-template <typename VT, int R, bool DELTA, int COLS>
-__global__ void __launch_bounds__(COLS * 4)
+template <typename VT, int R, bool DELTA, int COLS, int LANES>
+__global__ void __launch_bounds__(COLS * LANES)
 scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
             const VT* __restrict__ v, int ldv, const float* __restrict__ g, int ldg,
             const float* __restrict__ beta, int ldb, const float* __restrict__ decay,
@@ -195,15 +196,15 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
             const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
             const int* __restrict__ seq_qlen, int H, int rep, int dk, int dv, int vec16,
             ConvKeep keep) {
-    constexpr int PD = 4 * (R + 4);                  // a token's vector in shared memory
+    constexpr int PD = LANES * (R + 4);                  // a token's vector in shared memory
     constexpr int VECS = DELTA ? 3 : 2;              // q, k (, g)
     extern __shared__ __align__(16) float buf[];     // [2][TB][VECS][PD]
     const int s = blockIdx.x, h = blockIdx.y;
-    const int col = blockIdx.z * COLS + (threadIdx.x >> 2), l = threadIdx.x & 3;
+    const int col = blockIdx.z * COLS + threadIdx.x / LANES, l = threadIdx.x % LANES;
     const bool live = col < dv;
     const int qlen = seq_qlen[s], tok0 = seq_qstart[s];
     const int hk = h / rep;                          // the q/k head this head reads
-    for (int i = threadIdx.x; i < 2 * TB * VECS * PD; i += COLS * 4) buf[i] = 0.0f;
+    for (int i = threadIdx.x; i < 2 * TB * VECS * PD; i += COLS * LANES) buf[i] = 0.0f;
     __syncthreads();                                 // the padding stays zero from here on
     pdl_wait();
 
@@ -211,7 +212,7 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
     if (keep.K > 1) {                                // the sequence's blocks share the channels out
         float* cs = slot_state + keep.offset;
         const int rank = h * gridDim.z + blockIdx.z, blocks = H * gridDim.z;
-        for (int c = rank * (COLS * 4) + threadIdx.x; c < keep.C; c += blocks * (COLS * 4))
+        for (int c = rank * (COLS * LANES) + threadIdx.x; c < keep.C; c += blocks * (COLS * LANES))
             for (int i = 0; i < keep.K - 1; ++i) {   // ascending: what is read lies ahead
                 const int rel = qlen - (keep.K - 1) + i;
                 float x;
@@ -226,7 +227,7 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
     float S[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = state_row(r, l);
+        const int i = state_row<LANES>(r, l);
         S[r] = (live && i < dk) ? S_g[(size_t)i * dv + col] : 0.0f;
     }
     const float dec = DELTA ? 0.0f : decay[h];
@@ -236,20 +237,20 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
         const int count = min(TB, qlen - b * TB);
         if (vec16) {
             const int quads = dk >> 2;
-            for (int idx = threadIdx.x; idx < count * quads; idx += COLS * 4) {
+            for (int idx = threadIdx.x; idx < count * quads; idx += COLS * LANES) {
                 const int t = idx / quads, c = idx - t * quads;
                 const size_t tok = (size_t)(tok0 + b * TB + t);
-                float* d = dst + (size_t)t * VECS * PD + (c & 3) * (R + 4) + ((c >> 2) << 2);
+                float* d = dst + (size_t)t * VECS * PD + (c % LANES) * (R + 4) + ((c / LANES) << 2);
                 cp_async16(d, q + tok * ldq + hk * dk + 4 * c);
                 cp_async16(d + PD, k + tok * ldk + hk * dk + 4 * c);
                 if (DELTA) cp_async16(d + 2 * PD, g + tok * ldg + h * dk + 4 * c);
             }
         } else {
-            for (int idx = threadIdx.x; idx < count * dk; idx += COLS * 4) {
+            for (int idx = threadIdx.x; idx < count * dk; idx += COLS * LANES) {
                 const int t = idx / dk, i = idx - t * dk;
                 const size_t tok = (size_t)(tok0 + b * TB + t);
-                float* d = dst + (size_t)t * VECS * PD + ((i >> 2) & 3) * (R + 4) +
-                           ((i >> 4) << 2) + (i & 3);
+                float* d = dst + (size_t)t * VECS * PD + ((i >> 2) % LANES) * (R + 4) +
+                           (((i >> 2) / LANES) << 2) + (i & 3);
                 cp_async4(d, q + tok * ldq + hk * dk + i);
                 cp_async4(d + PD, k + tok * ldk + hk * dk + i);
                 if (DELTA) cp_async4(d + 2 * PD, g + tok * ldg + h * dk + i);
@@ -319,6 +320,7 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
                 float part = (p0 + p1) + (p2 + p3);
                 part += __shfl_xor_sync(0xffffffffu, part, 1);
                 part += __shfl_xor_sync(0xffffffffu, part, 2);
+                if (LANES == 8) part += __shfl_xor_sync(0xffffffffu, part, 4);
                 u = bt[t] * (vt[t] - part);
             } else {
                 u = vt[t];
@@ -336,6 +338,10 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
             kq += __shfl_xor_sync(0xffffffffu, kq, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);
             kq += __shfl_xor_sync(0xffffffffu, kq, 2);
+            if (LANES == 8) {
+                o += __shfl_xor_sync(0xffffffffu, o, 4);
+                kq += __shfl_xor_sync(0xffffffffu, kq, 4);
+            }
             o = fmaf(u, kq, o);
 #pragma unroll
             for (int r = 0; r < R / 4; ++r) {
@@ -354,7 +360,7 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
     if (live) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
-            const int i = state_row(r, l);
+            const int i = state_row<LANES>(r, l);
             if (i < dk) S_g[(size_t)i * dv + col] = S[r];
         }
     }
@@ -418,7 +424,7 @@ __global__ void mean_of_normed_kernel(const T* __restrict__ a, const T* __restri
     }
 }
 
-template <typename VT, bool DELTA, int COLS>
+template <typename VT, bool DELTA, int COLS, int LANES>
 int launch_scan_cols(int R, dim3 grid, cudaStream_t s, const float* q, int ldq, const float* k,
                      int ldk, const VT* v, int ldv, const float* g, int ldg, const float* beta,
                      int ldb, const float* decay, float* state, long long slot_stride, float* out,
@@ -426,21 +432,23 @@ int launch_scan_cols(int R, dim3 grid, cudaStream_t s, const float* q, int ldq, 
                      int rep, int dk, int dv, int vec16, ConvKeep keep) {
 #define SCAN(RR)                                                                                \
     do {                                                                                        \
-        const size_t smem = (size_t)2 * TB * (DELTA ? 3 : 2) * 4 * (RR + 4) * sizeof(float);    \
+        const size_t smem = (size_t)2 * TB * (DELTA ? 3 : 2) * LANES * (RR + 4) * sizeof(float); \
         if (smem > 48 * 1024) {                                                                 \
-            cudaError_t e = cudaFuncSetAttribute(scan_kernel<VT, RR, DELTA, COLS>,              \
+            cudaError_t e = cudaFuncSetAttribute(scan_kernel<VT, RR, DELTA, COLS, LANES>,       \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                                  (int)smem);                                    \
             if (e != cudaSuccess) return (int)e;                                                \
         }                                                                                       \
-        return de_launch(scan_kernel<VT, RR, DELTA, COLS>, grid, dim3(COLS * 4), smem, s, q,    \
-                         ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state, slot_stride,     \
-                         out, seq_slot, seq_qstart, seq_qlen, H, rep, dk, dv, vec16, keep);     \
+        return de_launch(scan_kernel<VT, RR, DELTA, COLS, LANES>, grid, dim3(COLS * LANES),     \
+                         smem, s, q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state,      \
+                         slot_stride, out, seq_slot, seq_qstart, seq_qlen, H, rep, dk, dv,      \
+                         vec16, keep);                                                          \
     } while (0)
     if (R <= 8) SCAN(8);
     if (R <= 16) SCAN(16);
     if (R <= 32) SCAN(32);
-    SCAN(64);
+    if (LANES == 4) SCAN(64);
+    return -6;
 #undef SCAN
 }
 
@@ -461,24 +469,27 @@ int launch_scan(cudaStream_t s, const float* q, int ldq, const float* k, int ldk
                 float* state, long long slot_stride, float* out, const int* seq_slot,
                 const int* seq_qstart, const int* seq_qlen, int n_seqs, int H, int rep, int dk,
                 int dv, ConvKeep keep) {
-    // rows go to the quarters in fours, sixteen at a time: a quarter holds 4 * ceil(dk / 16)
-    const int R = 4 * ((dk + 15) / 16);
     const int vec16 = (dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && (!DELTA || ldg % 4 == 0) &&
                        (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 &&
                        (!DELTA || (uintptr_t)g % 16 == 0)) ? 1 : 0;
+    const long long pairs = (long long)n_seqs * H;
+#define COLS_CASE(CC, LL)                                                                       \
+    return launch_scan_cols<VT, DELTA, CC, LL>(R, grid, s, q, ldq, k, ldk, v, ldv, g, ldg,      \
+                                               beta, ldb, decay, state, slot_stride, out,      \
+                                               seq_slot, seq_qstart, seq_qlen, H, rep, dk, dv, \
+                                               vec16, keep)
+    // (eight lanes a column - twice the warps, half the instructions a token and warp - was
+    // measured for a single long prompt and is slower: 867 against 788 us for 2,048 tokens of 16
+    // heads of 128 x 128; a token's time is its chain of dependent steps, which a third butterfly
+    // stage lengthens)
+    const int R = 4 * ((dk + 15) / 16);
     // narrower blocks while blocks of 32 columns would not give every SM two
     int cols = 32;
-    while (cols > 8 && (long long)n_seqs * H * ((dv + cols - 1) / cols) < 2LL * sm_count())
-        cols >>= 1;
-    if (dv <= 8) cols = 8; else if (dv <= 16 && cols > 16) cols = 16;
+    while (cols > 8 && pairs * ((dv + cols - 1) / cols) < 2LL * sm_count()) cols >>= 1;
     dim3 grid(n_seqs, H, (dv + cols - 1) / cols);
-#define COLS_CASE(CC)                                                                           \
-    return launch_scan_cols<VT, DELTA, CC>(R, grid, s, q, ldq, k, ldk, v, ldv, g, ldg, beta,    \
-                                           ldb, decay, state, slot_stride, out, seq_slot,      \
-                                           seq_qstart, seq_qlen, H, rep, dk, dv, vec16, keep)
-    if (cols == 8) COLS_CASE(8);
-    if (cols == 16) COLS_CASE(16);
-    COLS_CASE(32);
+    if (cols == 8) COLS_CASE(8, 4);
+    if (cols == 16) COLS_CASE(16, 4);
+    COLS_CASE(32, 4);
 #undef COLS_CASE
 }
 
