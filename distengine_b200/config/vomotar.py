@@ -78,10 +78,10 @@ def _parallel(m: Mapping[str, Any], where: str) -> tuple:
         raise ConfigError(f"config.json: '{wb}decay' must list one number for each of the "
                           f"{rheads} heads")
     rot = _section(b, "rot", wb)
-    dims = _int(rot, "dims", wb + "rot.")
-    if dims % 2 or dims > rdim:
-        raise ConfigError(f"config.json: '{wb}rot.dims' ({dims}) must be even and at most "
-                          f"'{wb}dim' ({rdim})")
+    dims = rot.get("dims")
+    if type(dims) is not int or dims < 0 or dims % 2 or dims > rdim:
+        raise ConfigError(f"config.json: '{wb}rot.dims' ({dims!r}) must be an even number from 0 "
+                          f"to '{wb}dim' ({rdim})")
     right = (rheads, rdim, _int(b, "vdim", wb), tuple(float(x) for x in decay), dims,
              _number(rot, "base", wb + "rot."))
     return ("parallel", left, right)
