@@ -859,8 +859,8 @@ def main() -> int:
         return 0
     points = {}
     # (batch 64 first and once more at the end: its step has two states, 1.33 and 1.41 ms, and
-    # with more than two other shapes of step replayed before it, it is mostly in the slow one -
-    # see the list of weak spots in DESIGN.md; both are reported)
+    # with more than two other shapes of step replayed before it, it is mostly in the slow one;
+    # both are reported)
     for b, name in ((64, "decode_b64"), (1, "decode_b1"), (16, "decode_b16"),
                     (64, "decode_b64_again")):
         b_ms, _, _, _ = decode(b, min(steps, NEW_TOKENS), warmup)

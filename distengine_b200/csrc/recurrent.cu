@@ -204,9 +204,13 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
     const bool live = col < dv;
     const int qlen = seq_qlen[s], tok0 = seq_qstart[s];
     const int hk = h / rep;                          // the q/k head this head reads
-    for (int i = threadIdx.x; i < 2 * TB * VECS * PD; i += COLS * LANES) buf[i] = 0.0f;
-    __syncthreads();                                 // the padding stays zero from here on
+    if (dk < LANES * R) {                            // rows beyond dk: their q, k, g stay zero
+        for (int i = threadIdx.x; i < 2 * TB * VECS * PD; i += COLS * LANES) buf[i] = 0.0f;
+        __syncthreads();
+    }
     pdl_wait();
+    // (The state through shared memory, so that memory sees whole rows of COLS columns, was
+    // measured and is slower: 92 against 55 us for 64 single tokens of 16 heads of 128 x 128.)
 
     float* slot_state = state + (size_t)seq_slot[s] * slot_stride;
     if (keep.K > 1) {                                // the sequence's blocks share the channels out
