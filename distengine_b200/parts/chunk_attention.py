@@ -88,7 +88,7 @@ class ChunkAttention(ProjectedMixer):
         prep.add(name, plan.items)
         prep.notes[self.key] = rows
 
-    def run(self, proj, ctx, cache):
+    def run(self, proj, ctx, cache, ahead=None):
         if cache is None or cache.kind != "paged":
             raise ValueError("chunk attention needs a paged key/value cache")
         n = proj.shape[0]
@@ -105,9 +105,7 @@ class ChunkAttention(ProjectedMixer):
                                ctx.arrays[self.key + "/items"], self.r1, self.r2, self.heads,
                                self.kv_heads, self.dk, self.dv, self.scale, self.chunk, ctx,
                                tile_rows=ctx.notes[self.key])
-        out = ctx.buffer("chunk_attention.out", (n, self.width))
-        ops.linear(context, self.w_o, out=out, status=ctx.status)
-        return out
+        return self.project_out(context, "chunk_attention.out", ctx, ahead)
 
 
 register_mixer("chunk_attention", ChunkAttention)

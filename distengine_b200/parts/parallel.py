@@ -18,7 +18,7 @@ from ..config.model import PartSpec
 from ..kernels import ops
 from ..kernels import recurrent as rk
 from .base import Mixer, build_mixer, compute_matrix, register_mixer
-from .context import CacheBinding, StepContext, StepPrep
+from .context import CacheBinding, StepContext, StepPrep, UnscaledRows
 from .recurrent import ProjectedMixer, stack_segments, vector32
 
 
@@ -66,13 +66,21 @@ class ParallelMixer(Mixer):
         for branch in self.branches:
             branch.prepare(prep)
 
-    def forward(self, x: torch.Tensor, ctx: StepContext,
+    def takes_unscaled(self, n_rows: int) -> bool:
+        """The norm before the mixer can ride on the one input product (``NormRider``); the
+        mixer's last operation is no product, so the norm after it runs itself."""
+        return ops.norm_ride_parts(n_rows, self.w_in, self.dtype) > 0
+
+    def forward(self, x: "torch.Tensor | UnscaledRows", ctx: StepContext,
                 cache: "CacheBinding | None") -> torch.Tensor:
         if cache is None or cache.kind != "parts" or len(cache.parts) != len(self.branches):
             raise ValueError("parallel: one cache binding per branch is needed")
+        before = None
+        if isinstance(x, UnscaledRows):
+            before, x = x, x.rows
         n = x.shape[0]
         proj = ctx.buffer("parallel.proj", (n, self.w_in.shape[0]))
-        ops.linear(x, self.w_in, out=proj, status=ctx.status)
+        ops.linear(x, self.w_in, out=proj, status=ctx.status, before=before)
         outs = [branch.run(proj[:, at: at + rows], ctx, binding)
                 for branch, at, rows, binding in zip(self.branches, self.offsets, self.rows,
                                                      cache.parts)]

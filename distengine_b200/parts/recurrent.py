@@ -34,7 +34,7 @@ import torch
 from ..kernels import ops
 from ..kernels import recurrent as rk
 from .base import Mixer, StateSpec, compute_matrix, register_mixer
-from .context import CacheBinding, StepContext
+from .context import CacheBinding, NormAhead, StepContext, UnscaledRows
 
 
 def _up8(n: int) -> int:
@@ -68,20 +68,49 @@ class ProjectedMixer(Mixer):
     def input_matrix(self) -> torch.Tensor:
         raise NotImplementedError
 
-    def run(self, proj: torch.Tensor, ctx: StepContext, cache: "CacheBinding | None") -> torch.Tensor:
+    def run(self, proj: torch.Tensor, ctx: StepContext, cache: "CacheBinding | None",
+            ahead: "NormAhead | None" = None) -> "torch.Tensor | None":
         raise NotImplementedError
 
     def finish_load(self) -> None:
         """Called by whoever owns the input product once the matrix is on the device elsewhere."""
         self._host_in = None
 
-    def forward(self, x: torch.Tensor, ctx: StepContext, cache: "CacheBinding | None") -> torch.Tensor:
+    def _own_input(self) -> torch.Tensor:
         if self.w_in is None:
             self.w_in = compute_matrix(self.input_matrix(), self.dtype, self.device)
             self.finish_load()
-        proj = ctx.buffer(f"{self.kind}.proj", (x.shape[0], self.w_in.shape[0]))
-        ops.linear(x, self.w_in, out=proj, status=ctx.status)
-        return self.run(proj, ctx, cache)
+        return self.w_in
+
+    # the norm before the mixer can ride on the input product, the norm after it on the output
+    # product (``parts.base.NormRider``), where those go to the weight-streaming kernels
+    def takes_unscaled(self, n_rows: int) -> bool:
+        return ops.norm_ride_parts(n_rows, self._own_input(), self.dtype) > 0
+
+    def ahead_parts(self, n_rows: int) -> int:
+        return ops.norm_ride_parts(n_rows, self.w_o, self.dtype)
+
+    def forward(self, x: "torch.Tensor | UnscaledRows", ctx: StepContext,
+                cache: "CacheBinding | None",
+                ahead: "NormAhead | None" = None) -> "torch.Tensor | None":
+        before = None
+        if isinstance(x, UnscaledRows):
+            before, x = x, x.rows
+        w_in = self._own_input()
+        proj = ctx.buffer(f"{self.kind}.proj", (x.shape[0], w_in.shape[0]))
+        ops.linear(x, w_in, out=proj, status=ctx.status, before=before)
+        return self.run(proj, ctx, cache, ahead=ahead)
+
+    def project_out(self, rows: torch.Tensor, name: str, ctx: StepContext,
+                    ahead: "NormAhead | None") -> "torch.Tensor | None":
+        """The output product; with ``ahead`` it joins the residual and does the next norm's
+        work (and nothing is returned)."""
+        if ahead is not None:
+            ops.linear(rows, self.w_o, out=ahead.rows, status=ctx.status, after=ahead)
+            return None
+        out = ctx.buffer(name, (rows.shape[0], self.width))
+        ops.linear(rows, self.w_o, out=out, status=ctx.status)
+        return out
 
 
 class GatedDeltaRule(ProjectedMixer):
@@ -144,7 +173,7 @@ class GatedDeltaRule(ProjectedMixer):
         # the state matrices, then the convolution's last taps - 1 inputs
         return StateSpec((self.state_rows + (self.taps - 1) * self.channels,), torch.float32)
 
-    def run(self, proj, ctx, cache):
+    def run(self, proj, ctx, cache, ahead=None):
         if cache is None or cache.kind != "state":
             raise ValueError("the gated delta rule needs a state slot")
         if not cache.writes:
@@ -170,9 +199,7 @@ class GatedDeltaRule(ProjectedMixer):
                       keep=(proj, self.state_rows, self.channels, self.taps))
         gated = ctx.buffer("delta.gated", (n, H * dv))
         rk.head_gate(o, gate, self.norm, gated, H, dv, self.eps)
-        out = ctx.buffer("delta.out", (n, self.width))
-        ops.linear(gated, self.w_o, out=out, status=ctx.status)
-        return out
+        return self.project_out(gated, "delta.out", ctx, ahead)
 
 
 class Retention(ProjectedMixer):
@@ -212,7 +239,7 @@ class Retention(ProjectedMixer):
     def cache_spec(self):
         return StateSpec((self.heads * self.dk * self.dv,), torch.float32)
 
-    def run(self, proj, ctx, cache):
+    def run(self, proj, ctx, cache, ahead=None):
         if cache is None or cache.kind != "state":
             raise ValueError("retention needs a state slot")
         if not cache.writes:
@@ -226,9 +253,7 @@ class Retention(ProjectedMixer):
                       dv, ctx, decay=self.decay)
         gated = ctx.buffer("retention.gated", (n, H * dv))
         rk.head_gate(o, proj[:, self.g_col: self.g_col + H * dv], None, gated, H, dv, self.eps)
-        out = ctx.buffer("retention.out", (n, self.width))
-        ops.linear(gated, self.w_o, out=out, status=ctx.status)
-        return out
+        return self.project_out(gated, "retention.out", ctx, ahead)
 
 
 register_mixer("gated_delta_rule", GatedDeltaRule)
