@@ -124,6 +124,32 @@ def test_long_decoding_with_graphs(dtype_name, model_root):
         _compare(rows, {"long": want}, DTYPES[dtype_name], f"long decode graphs={graphs}")
 
 
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_a_long_prompt_at_wide_sizes(dtype_name, model_root):
+    """1,100 tokens in one step (the products of a thousand rows and more, the attention's wide
+    tiles, four chunk edges), then tokens one by one, then the same prompt in two uneven portions."""
+    from distengine_b200.engine.replay import build_runner
+    name = "vomo_wide"
+    folder, weights = vc.make_folder(name, model_root)
+    ids = vc.tokens(name, 1112, 3)
+    act = None if dtype_name == "float32" else torch.bfloat16
+    want = pv.forward(vc.ALL[name], weights, ids, act=act).to(torch.float32).numpy()
+    picked = [0, 1, 299, 300, 301, 599, 600, 899, 900, 1023, 1024, 1099]
+    head = {"step": 0, "end": [], "entries": [{"id": "w", "tokens": ids[:1100], "want": picked}]}
+    tail = [{"step": 1 + i, "end": ["w"] if i == 11 else [],
+             "entries": [{"id": "w", "tokens": [ids[1100 + i]], "want": [0]}]} for i in range(12)]
+    cut = [{"step": 13, "end": [], "entries": [{"id": "c", "tokens": ids[:1027], "want": [1026]}]},
+           {"step": 14, "end": ["c"], "entries": [{"id": "c", "tokens": ids[1027:],
+                                                    "want": [0, 84]}]}]
+    steps = [head] + tail + cut
+    runner = build_runner(folder, dtype_name, 1152, page_size=16, poison_freed_pages=True)
+    with tempfile.TemporaryDirectory() as out:
+        th.replay_in_process(runner, steps, out)
+        rows = th.collect(steps, out, vc.ALL[name]["vocab"])
+    assert len(rows) == len(picked) + 12 + 3
+    _compare(rows, {"w": want, "c": want}, DTYPES[dtype_name], f"wide {dtype_name}")
+
+
 def test_batch_of_unequal_requests_against_each_alone(model_root):
     """Four unequal requests in one step give what each gives alone (32-bit: to rounding)."""
     from distengine_b200.engine.replay import build_runner
@@ -172,6 +198,30 @@ def test_greedy_generation_through_the_engine(model_root):
         logits = pv.forward(vc.ALL[name], weights, prompt)[-1]
         gap = (logits.max() - logits[tokens[0]]).item()
         assert gap <= 4e-2 * logits.abs().max().item()
+
+
+def test_preempted_requests_are_recomputed(model_root):
+    """So few pages that running requests are preempted: they give back pages and slot, and their
+    states are built again from their tokens; the greedy tokens stay the plain implementation's."""
+    from distengine_b200 import Engine, EngineConfig
+    name = "vomo_a"
+    folder, weights = vc.make_folder(name, model_root)
+    prompts = [vc.tokens(name, n, 60 + i) for i, n in enumerate((30, 27, 33))]
+    new = 24
+
+    def plain_greedy(prompt):
+        ids = list(prompt)
+        for _ in range(new):
+            ids.append(int(pv.forward(vc.ALL[name], weights, ids)[-1].argmax()))
+        return ids[len(prompt):]
+
+    engine = Engine(folder, EngineConfig(dtype="float32", block_size=16, num_blocks=5,
+                                         decode_batch_size=3, max_batch_tokens=48,
+                                         max_model_len=64))
+    assert engine.generate(prompts, new) == [plain_greedy(p) for p in prompts]
+    assert engine.scheduler.num_preemptions > 0
+    engine.cache.check_invariants()
+    assert not engine.cache.live
 
 
 def test_the_command_line_generates(model_root):

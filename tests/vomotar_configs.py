@@ -56,9 +56,19 @@ VOMO_C = {
     ],
 }
 
-ALL = {"vomo_a": VOMO_A, "vomo_b": VOMO_B, "vomo_c": VOMO_C}
-SEEDS = {"vomo_a": 5, "vomo_b": 6, "vomo_c": 7}
-PAGES = {"vomo_a": 16, "vomo_b": 8, "vomo_c": 32}
+# heads of 64 and 128 features, rows that are whole 16-byte pieces: the sizes at which prompts of a
+# thousand tokens and more take the tensor-core products, the wide attention tiles and 16-byte copies
+VOMO_WIDE = {
+    "architecture": "Vomotar", "vocab": 300, "width": 256, "norm": {"eps": 2e-6, "groups": 8},
+    "layers": [
+        _parallel((4, 2, 128, 64, 0.1, 300), (2, 64, 128, [0.999, 0.95], 32, 10000.0), 512),
+        _delta(4, 4, 64, 64, 4, 32, 512),
+    ],
+}
+
+ALL = {"vomo_a": VOMO_A, "vomo_b": VOMO_B, "vomo_c": VOMO_C, "vomo_wide": VOMO_WIDE}
+SEEDS = {"vomo_a": 5, "vomo_b": 6, "vomo_c": 7, "vomo_wide": 8}
+PAGES = {"vomo_a": 16, "vomo_b": 8, "vomo_c": 32, "vomo_wide": 16}
 
 
 def make_folder(name: str, root: str, weights: "dict | None" = None) -> "tuple[str, dict]":
