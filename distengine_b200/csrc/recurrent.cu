@@ -511,7 +511,16 @@ DE_EXPORT int de_delta_prep(int dtype, const void* proj, int ld, const float* a,
     if (H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || K <= 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = (size_t)2 * G * dk * sizeof(float);
-    if (smem > 48 * 1024) return -3;
+    if (smem > 200 * 1024) return -3;
+    if (smem > 48 * 1024) {
+        const cudaError_t e =
+            dtype == DE_BF16
+                ? cudaFuncSetAttribute(delta_prep_kernel<__nv_bfloat16>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                : cudaFuncSetAttribute(delta_prep_kernel<float>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
     // a block a token: many threads, so that a token of a decode step is a few rounds of loads
     // (with few tokens: steps of many tokens fill the GPU with blocks of 256)
     const int work = 2 * G * dk + H * dv;
