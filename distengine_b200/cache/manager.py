@@ -349,7 +349,9 @@ class CacheManager:
                 continue
             table = group.tables[request_id]
             first = min(self._first_needed(group, new_len), len(table))
-            gone = [p for p in range(first) if table[p] >= 0]
+            # the pages of the first keys that a window keeps stay
+            kept = (group.spec.keep_first + self.page_size - 1) // self.page_size
+            gone = [p for p in range(kept, first) if table[p] >= 0]
             if gone:
                 self._give(group, [table[p] for p in gone])
                 row = group.host_table[live.slot]

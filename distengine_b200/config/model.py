@@ -87,6 +87,16 @@ class ModelConfig:
     def tied_output(self) -> bool:
         raise NotImplementedError
 
+    @property
+    def embedding_scale(self) -> float:
+        """The embedding rows are multiplied by this as they enter the residual stream."""
+        return 1.0
+
+    @property
+    def logit_softcap(self) -> "float | None":
+        """A number c: logits <- c * tanh(logits / c).  None: the logits as they are."""
+        return None
+
     # -- the model as data
     def layer_specs(self) -> list[LayerSpec]:
         raise NotImplementedError

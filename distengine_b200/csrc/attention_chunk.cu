@@ -13,6 +13,16 @@
 // so a row's result does not depend, bit for bit, on what shares its tile, its step or its batch.
 // The host's work items are those of the other attention kernels (kernels/attention_plan.py),
 // unsplit: a chunk bounds every key range.
+//
+// The same kernels also serve attention whose keys are bounded by a sliding window that keeps the
+// first tokens of the sequence, with a soft cap on the scores (`Sight`):
+//
+//   token i sees key j when j <= i and (i - j < window or j < keep_first)
+//   score <- softcap * tanh(score / softcap)
+//
+// A block then walks the tiles of the kept first keys and jumps to the tile in which its rows'
+// windows begin.  r1 / r2 null: no distance penalty.  `out_f32`: the rows' results are written as
+// float32 (for a kernel that turns them by position or gates them before they are rounded).
 
 #include "common.cuh"
 
@@ -27,6 +37,52 @@ constexpr int MAX_D = 256;
 struct WorkItem {
     int seq, row0, kv_begin, kv_end, partial, pad0, pad1, pad2;
 };
+
+// Which keys a row sees besides j <= i, and what happens to its scores.
+struct Sight {
+    int chunk;          // > 0: keys of the row's own chunk of positions only
+    int window;         // > 0: the last `window` keys only ...
+    int keep_first;     // ... and the first `keep_first` keys of the sequence
+    float softcap;      // > 0: score <- softcap * tanh(score / softcap)
+};
+
+// first key of the near range of a row at `pos` (does not fall as pos grows)
+__device__ __forceinline__ int sight_lo(const Sight& m, int pos) {
+    int lo = 0;
+    if (m.chunk > 0) lo = pos / m.chunk * m.chunk;
+    if (m.window > 0) lo = max(lo, pos - m.window + 1);
+    return lo;
+}
+// keys [0, this) are seen as well
+__device__ __forceinline__ int sight_first(const Sight& m, int lo) {
+    return (m.window > 0 && m.keep_first > 0) ? min(m.keep_first, lo) : 0;
+}
+__device__ __forceinline__ float sight_score(const Sight& m, float s, float scale, float pen1,
+                                             float pen2, bool penalty, float dist) {
+    s *= scale;
+    if (penalty) s -= pen1 * log1pf(pen2 * dist);
+    if (m.softcap > 0.0f) s = m.softcap * tanhf(s / m.softcap);
+    return s;
+}
+// The tiles a block walks: those of the kept first keys [0, kf), then from the tile of `lo` on.
+struct TileWalk {
+    int start, jump_at, jump_to;
+    __device__ __forceinline__ TileWalk(int lo, int kf, int tile) {
+        const int near = (lo / tile) * tile, first_end = ((kf + tile - 1) / tile) * tile;
+        start = kf > 0 ? 0 : near;
+        jump_at = (kf > 0 && first_end < near) ? first_end : -1;
+        jump_to = near;
+    }
+    __device__ __forceinline__ int next(int kt, int tile) const {
+        const int n = kt + tile;
+        return n == jump_at ? jump_to : n;
+    }
+};
+template <typename T>
+__device__ __forceinline__ void store_out(void* out, int out_f32, size_t at, float x) {
+    if (out_f32) ((float*)out)[at] = x;
+    else ((T*)out)[at] = from_float<T>(x);
+}
 
 // k copied, v divided by its root mean square over the head (eps inside the root), both into the
 // pages.  proj row = [... | k (G dk) | v (G dv)] from column k_col on.  grid (tokens, kv heads).
@@ -61,16 +117,137 @@ __global__ void kv_write_normed_kernel(const T* __restrict__ proj, int ld, int k
         v_pages[at * dv + i] = from_float<T>(to_float(vs[i]) * inv);
 }
 
+// Queries and keys turned by position, values turned by position over all their features, keys
+// and values into the pages.  proj row = [q (H dk) | k (G dk) | v (G dv) | ...] (a run that reads
+// another run's cache has q only: write_kv 0).  Pairs are (i, i + n/2) of the first n features:
+// n = rot with the angles pos * fk[i] for q and k, n = dv with pos * fv[i] for v (fv null: values
+// are stored as they are).  q is turned in place.  One block a token.
+template <typename T>
+__global__ void kv_write_rotated_kernel(T* __restrict__ proj, int ld, const int* __restrict__ positions,
+                                        const int* __restrict__ token_slot,
+                                        const float* __restrict__ fk, int rot,
+                                        const float* __restrict__ fv, int H, int G, int dk, int dv,
+                                        T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                        const int* __restrict__ block_table, int table_stride,
+                                        int page, int num_pages, int write_kv,
+                                        int* __restrict__ status) {
+    const int n = blockIdx.x;
+    const int pos = positions[n];
+    const float fpos = (float)pos;
+    T* row = proj + (size_t)n * ld;
+    const int half = rot / 2, per = dk - half;       // work items a head: pairs, then plain features
+    size_t at = 0;
+    bool can_write = write_kv != 0;
+    if (can_write) {
+        const int page_id = block_table[(size_t)token_slot[n] * table_stride + pos / page];
+        if (page_id < 0 || page_id >= num_pages) {   // never written outside the pool
+            if (threadIdx.x == 0) atomicExch(status, 1);
+            can_write = false;
+        }
+        at = ((size_t)page_id * G) * page + (size_t)(pos % page);
+    }
+    pdl_wait();
+    const int qk_heads = H + (write_kv ? G : 0);
+    for (int idx = threadIdx.x; idx < qk_heads * per; idx += blockDim.x) {
+        const int h = idx / per, i = idx - h * per;
+        T* src = row + h * dk;
+        T* dst = src;                                // q in place
+        if (h >= H) {
+            if (!can_write) continue;
+            dst = k_pages + (at + (size_t)(h - H) * page) * dk;
+        }
+        if (i < half) {
+            float sn, cs, ra, rb;
+            sincosf(fpos * fk[i], &sn, &cs);
+            rope_rotate(to_float(src[i]), to_float(src[i + half]), cs, sn, ra, rb);
+            dst[i] = from_float<T>(ra);
+            dst[i + half] = from_float<T>(rb);
+        } else if (h >= H) {
+            dst[i + half] = src[i + half];
+        }
+    }
+    if (can_write) {
+        const T* vs = row + (H + G) * dk;
+        if (fv != nullptr) {
+            const int vhalf = dv / 2, vper = dv - vhalf;
+            for (int idx = threadIdx.x; idx < G * vper; idx += blockDim.x) {
+                const int h = idx / vper, i = idx - h * vper;
+                const T* src = vs + h * dv;
+                T* dst = v_pages + (at + (size_t)h * page) * dv;
+                if (i < vhalf) {
+                    float sn, cs, ra, rb;
+                    sincosf(fpos * fv[i], &sn, &cs);
+                    rope_rotate(to_float(src[i]), to_float(src[i + vhalf]), cs, sn, ra, rb);
+                    dst[i] = from_float<T>(ra);
+                    dst[i + vhalf] = from_float<T>(rb);
+                } else {
+                    dst[i + vhalf] = src[i + vhalf];
+                }
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < G * dv; idx += blockDim.x) {
+                const int h = idx / dv, i = idx - h * dv;
+                v_pages[(at + (size_t)h * page) * dv + i] = vs[idx];
+            }
+        }
+    }
+    pdl_trigger();
+}
+
+// After the attention: every head's result (float32 [N, H dv]) turned back by its token's position
+// (pairs (i, i + dv/2), angle -pos * fv[i]; fv null: as it is), times sigmoid(gate) where a gate
+// (type T, row stride ld_gate) is given, rounded to the activation type.  One block a token.
+template <typename T>
+__global__ void attn_finish_kernel(const float* __restrict__ o, const int* __restrict__ positions,
+                                   const float* __restrict__ fv, const T* __restrict__ gate,
+                                   int ld_gate, T* __restrict__ out, int H, int dv) {
+    const int n = blockIdx.x;
+    const float fpos = (float)positions[n];
+    const float* src = o + (size_t)n * H * dv;
+    T* dst = out + (size_t)n * H * dv;
+    const T* gt = gate ? gate + (size_t)n * ld_gate : nullptr;
+    pdl_wait();
+    pdl_trigger();
+    if (fv != nullptr) {
+        const int half = dv / 2, per = dv - half;
+        for (int idx = threadIdx.x; idx < H * per; idx += blockDim.x) {
+            const int h = idx / per, i = idx - h * per;
+            const int a = h * dv + i, b = a + half;
+            if (i < half) {
+                float sn, cs, ra, rb;
+                sincosf(fpos * fv[i], &sn, &cs);
+                rope_rotate(src[a], src[b], cs, -sn, ra, rb);
+                if (gt) {
+                    ra *= 1.0f / (1.0f + expf(-to_float(gt[a])));
+                    rb *= 1.0f / (1.0f + expf(-to_float(gt[b])));
+                }
+                dst[a] = from_float<T>(ra);
+                dst[b] = from_float<T>(rb);
+            } else {
+                float x = src[b];
+                if (gt) x *= 1.0f / (1.0f + expf(-to_float(gt[b])));
+                dst[b] = from_float<T>(x);
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < H * dv; idx += blockDim.x) {
+            float x = src[idx];
+            if (gt) x *= 1.0f / (1.0f + expf(-to_float(gt[idx])));
+            dst[idx] = from_float<T>(x);
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(ROWS * 32)
-attn_chunk_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+attn_chunk_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ out, int out_stride,
                   const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                   const int* __restrict__ block_table, int table_stride, int num_pages,
                   const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
                   const int* __restrict__ seq_qlen, const int* __restrict__ seq_pos0,
                   const WorkItem* __restrict__ items, const float* __restrict__ r1,
                   const float* __restrict__ r2, int heads, int kv_heads, int dk, int dv, int page,
-                  float scale, int chunk, int* __restrict__ status) {
+                  float scale, Sight sight, int out_f32, int* __restrict__ status) {
     extern __shared__ float smem[];
     float* Ks = smem;                       // [TILE][dk + 1]; column dk: 0, or -inf without a page
     float* Vs = Ks + TILE * (dk + 1);       // [TILE][dv]
@@ -93,22 +270,24 @@ attn_chunk_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, in
     const int t = active ? r / g : 0;
     const int hq = hk * g + (active ? r % g : 0);
     const int pos = pos0 + t;
-    const float pen1 = r1[hq], pen2 = r2[hq];
+    const bool penalty = r1 != nullptr;
+    const float pen1 = penalty ? r1[hq] : 0.0f, pen2 = penalty ? r2[hq] : 0.0f;
 
     pdl_wait();
     for (int i = lane; i < dk; i += 32)
         Qs[warp * dk + i] = active ? to_float(q[(size_t)(tok0 + t) * q_stride + hq * dk + i]) : 0.0f;
 
-    // the tile's key range: from the chunk of its first token to its last token
+    // the tile's key range: from the chunk or window of its first token to its last token, and
+    // the kept first keys
     const int last_row = min(it.row0 + ROWS, rows_total) - 1;
     const int max_pos = pos0 + last_row / g, min_pos = pos0 + it.row0 / g;
     const int k_hi = min(it.kv_end, max_pos + 1);
-    int k_lo_true = it.kv_begin;
-    if (chunk > 0) k_lo_true = max(k_lo_true, min_pos / chunk * chunk);
-    const int k_lo = (k_lo_true / TILE) * TILE;
+    const int k_lo_true = max(it.kv_begin, sight_lo(sight, min_pos));
+    const int k_first = it.kv_begin > 0 ? 0 : sight_first(sight, k_lo_true);
+    const TileWalk walk(k_lo_true, k_first, TILE);
     // this row's
-    int row_lo = it.kv_begin;
-    if (chunk > 0) row_lo = max(row_lo, pos / chunk * chunk);
+    const int row_lo = max(it.kv_begin, sight_lo(sight, pos));
+    const int row_first = it.kv_begin > 0 ? 0 : sight_first(sight, row_lo);
     const int row_hi = min(it.kv_end, pos + 1);
 
     float m = -INFINITY, l = 0.0f;
@@ -116,11 +295,11 @@ attn_chunk_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, in
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) acc[i] = 0.0f;
 
-    for (int kt = k_lo; kt < k_hi; kt += TILE) {
+    for (int kt = walk.start; kt < k_hi; kt = walk.next(kt, TILE)) {
         __syncthreads();
         for (int j = warp; j < TILE; j += ROWS) {        // a warp a key: whole rows of the pages
             const int kpos = kt + j;
-            bool held = true, inside = kpos >= k_lo_true && kpos < k_hi;
+            bool held = true, inside = (kpos >= k_lo_true || kpos < k_first) && kpos < k_hi;
             size_t at = 0;
             if (inside) {
                 const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
@@ -142,11 +321,11 @@ attn_chunk_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, in
 
         const int kpos = kt + lane;
         const float* kr = Ks + lane * (dk + 1);
-        const bool valid = kpos >= row_lo && kpos < row_hi && kr[dk] == 0.0f;
+        const bool valid = (kpos >= row_lo || kpos < row_first) && kpos < row_hi && kr[dk] == 0.0f;
         const float* qr = Qs + warp * dk;
         float s = 0.0f;
         for (int i = 0; i < dk; ++i) s = fmaf(qr[i], kr[i], s);
-        s = valid ? s * scale - pen1 * log1pf(pen2 * (float)(pos - kpos)) : -INFINITY;
+        s = valid ? sight_score(sight, s, scale, pen1, pen2, penalty, (float)(pos - kpos)) : -INFINITY;
         const float m_new = fmaxf(m, warp_max(s));
         if (m_new == -INFINITY) continue;
         const float p = valid ? expf(s - m_new) : 0.0f;
@@ -169,11 +348,11 @@ attn_chunk_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, in
     pdl_trigger();
     if (!active) return;
     const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-    T* o = out + (size_t)(tok0 + t) * out_stride + hq * dv;
+    const size_t o = (size_t)(tok0 + t) * out_stride + hq * dv;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) {
         const int dd = lane + 32 * i;
-        if (dd < dv) o[dd] = from_float<T>(acc[i] * inv);
+        if (dd < dv) store_out<T>(out, out_f32, o + dd, acc[i] * inv);
     }
 }
 
@@ -207,14 +386,14 @@ template <> struct Piece<__nv_bfloat16> {
 
 template <typename T, int RW, int NCH>
 __global__ void __launch_bounds__(ROWS * 32, NCH <= 4 ? 2 : 1)
-attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
+attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ out, int out_stride,
                       const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                       const int* __restrict__ block_table, int table_stride, int num_pages,
                       const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
                       const int* __restrict__ seq_qlen, const int* __restrict__ seq_pos0,
                       const WorkItem* __restrict__ items, const float* __restrict__ r1,
                       const float* __restrict__ r2, int heads, int kv_heads, int dk, int dv,
-                      int page, float scale, int chunk, int* __restrict__ status) {
+                      int page, float scale, Sight sight, int out_f32, int* __restrict__ status) {
     constexpr int PN = Piece<T>::N;
     extern __shared__ __align__(16) float smem[];
     const int ks = ((dk + 31) / 32) * 32 + 4;       // a key's stride: float4 reads without conflicts
@@ -236,9 +415,10 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     bool active[RW];
-    int tok[RW], hq[RW], pos[RW], row_lo[RW], row_hi[RW];
+    int tok[RW], hq[RW], pos[RW], row_lo[RW], row_hi[RW], row_first[RW];
     float pen1[RW], pen2[RW], m[RW], l[RW];
     bool any = false;
+    const bool penalty = r1 != nullptr;
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
         const int r = it.row0 + warp * RW + i;
@@ -247,10 +427,10 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
         tok[i] = active[i] ? r / g : 0;
         hq[i] = hk * g + (active[i] ? r % g : 0);
         pos[i] = pos0 + tok[i];
-        pen1[i] = r1[hq[i]];
-        pen2[i] = r2[hq[i]];
-        row_lo[i] = it.kv_begin;
-        if (chunk > 0) row_lo[i] = max(row_lo[i], pos[i] / chunk * chunk);
+        pen1[i] = penalty ? r1[hq[i]] : 0.0f;
+        pen2[i] = penalty ? r2[hq[i]] : 0.0f;
+        row_lo[i] = max(it.kv_begin, sight_lo(sight, pos[i]));
+        row_first[i] = it.kv_begin > 0 ? 0 : sight_first(sight, row_lo[i]);
         row_hi[i] = min(it.kv_end, pos[i] + 1);
         m[i] = -INFINITY;
         l[i] = 0.0f;
@@ -258,9 +438,9 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
     const int last_row = min(it.row0 + ROWS * RW, rows_total) - 1;
     const int max_pos = pos0 + last_row / g, min_pos = pos0 + it.row0 / g;
     const int k_hi = min(it.kv_end, max_pos + 1);
-    int k_lo_true = it.kv_begin;
-    if (chunk > 0) k_lo_true = max(k_lo_true, min_pos / chunk * chunk);
-    const int k_lo = (k_lo_true / TILE) * TILE;
+    const int k_lo_true = max(it.kv_begin, sight_lo(sight, min_pos));
+    const int k_first = it.kv_begin > 0 ? 0 : sight_first(sight, k_lo_true);
+    const TileWalk walk(k_lo_true, k_first, TILE);
 
     const int ck = dk / PN, cv = dv / PN, per_key = ck + cv;
     uint4 pre[NCH];
@@ -276,7 +456,7 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
             if (e >= TILE * per_key) continue;
             const int j = e / per_key, w = e - j * per_key;
             const int kpos = kt + j;
-            if (kpos < k_lo_true || kpos >= k_hi) continue;
+            if ((kpos < k_lo_true && kpos >= k_first) || kpos >= k_hi) continue;
             const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
             if (page_id < 0 || page_id >= num_pages) {
                 missing |= 1u << c;
@@ -287,7 +467,7 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
             pre[c] = *reinterpret_cast<const uint4*>(src);
         }
     };
-    prefetch(k_lo);
+    prefetch(walk.start);
 #pragma unroll
     for (int i = 0; i < RW; ++i)
         for (int d = lane; d < dk; d += 32)
@@ -302,7 +482,7 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[i][b][e] = 0.0f;
 
-    for (int kt = k_lo; kt < k_hi; kt += TILE) {
+    for (int kt = walk.start; kt < k_hi; kt = walk.next(kt, TILE)) {
         __syncthreads();                             // the tile before this one has been used
 #pragma unroll
         for (int c = 0; c < NCH; ++c) {
@@ -322,7 +502,7 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
             }
         }
         __syncthreads();
-        if (kt + TILE < k_hi) prefetch(kt + TILE);   // in flight while this tile is worked on
+        if (walk.next(kt, TILE) < k_hi) prefetch(walk.next(kt, TILE));   // in flight meanwhile
         if (!any) continue;
 
         const int kpos = kt + lane;
@@ -347,8 +527,10 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
         bool some = false;
 #pragma unroll
         for (int i = 0; i < RW; ++i) {
-            const bool valid = active[i] && kpos >= row_lo[i] && kpos < row_hi[i] && held;
-            const float sc = valid ? s[i] * scale - pen1[i] * log1pf(pen2[i] * (float)(pos[i] - kpos))
+            const bool valid = active[i] && (kpos >= row_lo[i] || kpos < row_first[i]) &&
+                               kpos < row_hi[i] && held;
+            const float sc = valid ? sight_score(sight, s[i], scale, pen1[i], pen2[i], penalty,
+                                                 (float)(pos[i] - kpos))
                                    : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(sc));
             if (m_new == -INFINITY) {               // nothing of this tile is visible to the row
@@ -398,13 +580,14 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
     for (int i = 0; i < RW; ++i) {
         if (!active[i]) continue;
         const float inv = l[i] > 0.0f ? 1.0f / l[i] : 0.0f;
-        T* o = out + (size_t)(tok0 + tok[i]) * out_stride + hq[i] * dv;
+        const size_t o = (size_t)(tok0 + tok[i]) * out_stride + hq[i] * dv;
 #pragma unroll
         for (int b = 0; b < MAX_D / 128; ++b) {
             const int dd = 4 * lane + 128 * b;
             if (dd < dv) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) o[dd + e] = from_float<T>(acc[i][b][e] * inv);
+                for (int e = 0; e < 4; ++e)
+                    store_out<T>(out, out_f32, o + dd + e, acc[i][b][e] * inv);
             }
         }
     }
@@ -428,14 +611,14 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
 
 template <typename T, int RW>
 __global__ void __launch_bounds__(ROWS * 32)
-attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out,
+attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ out,
                          int out_stride, const T* __restrict__ k_pages,
                          const T* __restrict__ v_pages, const int* __restrict__ block_table,
                          int table_stride, int num_pages, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_qstart, const int* __restrict__ seq_pos0,
                          const float* __restrict__ r1, const float* __restrict__ r2, int heads,
-                         int kv_heads, int dk, int dv, int page, float scale, int chunk,
-                         int* __restrict__ status) {
+                         int kv_heads, int dk, int dv, int page, float scale, Sight sight,
+                         int out_f32, int* __restrict__ status) {
     constexpr int PN = Piece<T>::N;
     extern __shared__ __align__(16) float smem[];
     float* Qs = smem;                                // [RW][dk]
@@ -452,13 +635,19 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     const int g = heads / kv_heads;
     const int pos = seq_pos0[seq], slot = seq_slot[seq], tok = seq_qstart[seq];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int lo = chunk > 0 ? pos / chunk * chunk : 0, hi = pos + 1;
+    const int lo = sight_lo(sight, pos), hi = pos + 1, first = sight_first(sight, lo);
+    // the tiles: those of the kept first keys, then from the tile of `lo` on, dealt out in turn
+    const TileWalk walk(lo, first, TILE);
+    const int first_tiles = walk.jump_at > 0 ? walk.jump_at / TILE : 0;
+    const int near0 = walk.jump_at > 0 ? walk.jump_to : walk.start;
+    const int n_tiles = first_tiles + (hi - near0 + TILE - 1) / TILE;
+    const bool penalty = r1 != nullptr;
     float pen1[RW], pen2[RW], m[RW], l[RW];
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
         const int hq = hk * g + min(i, g - 1);
-        pen1[i] = r1[hq];
-        pen2[i] = r2[hq];
+        pen1[i] = penalty ? r1[hq] : 0.0f;
+        pen2[i] = penalty ? r2[hq] : 0.0f;
         m[i] = -INFINITY;
         l[i] = 0.0f;
     }
@@ -474,9 +663,10 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 #pragma unroll
         for (int b = 0; b < MAX_D / 32; ++b) acc[i][b] = 0.0f;
 
-    for (int kt = (lo / TILE) * TILE + warp * TILE; kt < hi; kt += ROWS * TILE) {
+    for (int ti = warp; ti < n_tiles; ti += ROWS) {
+        const int kt = ti < first_tiles ? ti * TILE : near0 + (ti - first_tiles) * TILE;
         const int kpos = kt + lane;
-        bool valid = kpos >= lo && kpos < hi;
+        bool valid = (kpos >= lo || kpos < first) && kpos < hi;
         size_t row = 0;
         if (valid) {
             const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
@@ -533,7 +723,8 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
         const float dist = (float)(pos - kpos);
 #pragma unroll
         for (int i = 0; i < RW; ++i) {
-            const float sc = valid ? s[i] * scale - pen1[i] * log1pf(pen2[i] * dist) : -INFINITY;
+            const float sc = valid ? sight_score(sight, s[i], scale, pen1[i], pen2[i], penalty, dist)
+                                   : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(sc));
             if (m_new == -INFINITY) {
                 p[i] = 0.0f;
@@ -600,11 +791,11 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
             }
         }
         const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-        T* o = out + (size_t)tok * out_stride + (hk * g + i) * dv;
+        const size_t o = (size_t)tok * out_stride + (hk * g + i) * dv;
 #pragma unroll
         for (int b = 0; b < MAX_D / 32; ++b) {
             const int dd = lane + 32 * b;
-            if (dd < dv) o[dd] = from_float<T>(res[b] * inv);
+            if (dd < dv) store_out<T>(out, out_f32, o + dd, res[b] * inv);
         }
     }
 }
@@ -643,8 +834,10 @@ DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void*
                                    const int* seq_slot, const int* seq_qstart,
                                    const int* seq_pos0, int n_seqs, const float* r1,
                                    const float* r2, int heads, int kv_heads, int dk, int dv,
-                                   int page, float scale, int chunk, int* status, void* stream) {
+                                   int page, float scale, int chunk, int window, int keep_first,
+                                   float softcap, int out_f32, int* status, void* stream) {
     if (n_seqs <= 0) return 0;
+    const Sight sight = {chunk, window, keep_first, softcap};
     if (!de_attn_chunk_decode_ok(dtype, heads, kv_heads, dk, dv) || (uintptr_t)k_pages % 16 != 0)
         return -2;
     cudaStream_t s = (cudaStream_t)stream;
@@ -662,10 +855,10 @@ DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void*
             if (e != cudaSuccess) return (int)e;                                                \
         }                                                                                       \
         return de_launch(attn_chunk_decode_kernel<T, RW>, grid, dim3(ROWS * 32), smem, s,       \
-                         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages,         \
+                         (const T*)q, q_stride, out, out_stride, (const T*)k_pages,             \
                          (const T*)v_pages, block_table, table_stride, num_pages, seq_slot,     \
                          seq_qstart, seq_pos0, r1, r2, heads, kv_heads, dk, dv, page, scale,    \
-                         chunk, status);                                                        \
+                         sight, out_f32, status);                                               \
     } while (0)
 #define DEC_T(T)                                                                                \
     do {                                                                                        \
@@ -699,14 +892,51 @@ DE_EXPORT int de_kv_write_normed(int dtype, const void* proj, int ld, int k_col,
                      status);
 }
 
+DE_EXPORT int de_kv_write_rotated(int dtype, void* proj, int ld, const int* positions,
+                                  const int* token_slot, const float* fk, int rot, const float* fv,
+                                  int H, int G, int dk, int dv, void* k_pages, void* v_pages,
+                                  const int* block_table, int table_stride, int page,
+                                  int num_pages, int write_kv, int n, int* status, void* stream) {
+    if (n <= 0) return 0;
+    if (rot < 0 || rot % 2 || rot > dk || (fv != nullptr && dv % 2)) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int work = (H + G) * dk + G * dv;
+    const int threads = n >= 512 ? 128 : (work >= 2048 ? 512 : 256);
+    if (dtype == DE_BF16)
+        return de_launch(kv_write_rotated_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s,
+                         (__nv_bfloat16*)proj, ld, positions, token_slot, fk, rot, fv, H, G, dk, dv,
+                         (__nv_bfloat16*)k_pages, (__nv_bfloat16*)v_pages, block_table,
+                         table_stride, page, num_pages, write_kv, status);
+    return de_launch(kv_write_rotated_kernel<float>, dim3(n), dim3(threads), 0, s, (float*)proj, ld,
+                     positions, token_slot, fk, rot, fv, H, G, dk, dv, (float*)k_pages,
+                     (float*)v_pages, block_table, table_stride, page, num_pages, write_kv, status);
+}
+
+DE_EXPORT int de_attn_finish(int dtype, const float* o, const int* positions, const float* fv,
+                             const void* gate, int ld_gate, void* out, int n, int H, int dv,
+                             void* stream) {
+    if (n <= 0) return 0;
+    if (fv != nullptr && dv % 2) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = n >= 512 ? 128 : (H * dv >= 2048 ? 512 : 256);
+    if (dtype == DE_BF16)
+        return de_launch(attn_finish_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s, o,
+                         positions, fv, (const __nv_bfloat16*)gate, ld_gate, (__nv_bfloat16*)out, H,
+                         dv);
+    return de_launch(attn_finish_kernel<float>, dim3(n), dim3(threads), 0, s, o, positions, fv,
+                     (const float*)gate, ld_gate, (float*)out, H, dv);
+}
+
 DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, int out_stride,
                             const void* k_pages, const void* v_pages, const int* block_table,
                             int table_stride, int num_pages, const int* seq_slot,
                             const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
                             const int* items, int num_items, const float* r1, const float* r2,
                             int heads, int kv_heads, int dk, int dv, int page, float scale,
-                            int chunk, int tile_rows, int* status, void* stream) {
+                            int chunk, int window, int keep_first, float softcap, int out_f32,
+                            int tile_rows, int* status, void* stream) {
     if (num_items <= 0) return 0;
+    const Sight sight = {chunk, window, keep_first, softcap};
     if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D || heads % kv_heads != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     if (tile_rows != ROWS && !(tile_rows == ROWS * 4 && vec_ok(dtype, dk, dv))) return -5;
@@ -727,10 +957,10 @@ DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, i
             if (ve != cudaSuccess) return (int)ve;                                              \
         }                                                                                       \
         return de_launch(attn_chunk_vec_kernel<T, RW, NCH>, vgrid, dim3(ROWS * 32), vsmem, s,   \
-                         (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages,         \
+                         (const T*)q, q_stride, out, out_stride, (const T*)k_pages,             \
                          (const T*)v_pages, block_table, table_stride, num_pages, seq_slot,     \
                          seq_qstart, seq_qlen, seq_pos0, (const WorkItem*)items, r1, r2, heads, \
-                         kv_heads, dk, dv, page, scale, chunk, status);                         \
+                         kv_heads, dk, dv, page, scale, sight, out_f32, status);                \
     } while (0)
 #define VEC_N(T, RW)                                                                            \
     do {                                                                                        \
@@ -759,10 +989,10 @@ DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, i
             if (e != cudaSuccess) return (int)e;                                                \
         }                                                                                       \
         return de_launch(attn_chunk_kernel<T>, grid, dim3(ROWS * 32), smem, s, (const T*)q,     \
-                         q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages,   \
+                         q_stride, out, out_stride, (const T*)k_pages, (const T*)v_pages,       \
                          block_table, table_stride, num_pages, seq_slot, seq_qstart, seq_qlen,  \
                          seq_pos0, (const WorkItem*)items, r1, r2, heads, kv_heads, dk, dv, page, \
-                         scale, chunk, status);                                                 \
+                         scale, sight, out_f32, status);                                        \
     } while (0)
     if (dtype == DE_BF16) LAUNCH(__nv_bfloat16);
     LAUNCH(float);

@@ -13,11 +13,11 @@
 DE_DEFINE_PDL_SWITCH
 
 // ------------------------------------------------------------------------------------------
-// embedding: out[n, :] = float(table[ids[n], :])           (the residual stream starts here)
+// embedding: out[n, :] = float(table[ids[n], :]) * scale   (the residual stream starts here)
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                  float* __restrict__ out, int width, int vocab) {
+                                  float* __restrict__ out, int width, int vocab, float scale) {
     const int n = blockIdx.x;
     int id = ids[n];
     if (id < 0 || id >= vocab) id = 0;          // ids are validated on the host; never read outside
@@ -25,19 +25,19 @@ __global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restri
     float* dst = out + (size_t)n * width;
     pdl_wait();                                  // the last step's kernels may still read `out`
     pdl_trigger();
-    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_float(row[i]) * scale;
 }
 
 DE_EXPORT int de_embed_rows(int dtype, const int* ids, const void* table, float* out, int n,
-                            int width, int vocab, void* stream) {
+                            int width, int vocab, float scale, void* stream) {
     if (n <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == DE_BF16)
         return de_launch(embed_rows_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s, ids,
-                         (const __nv_bfloat16*)table, out, width, vocab);
+                         (const __nv_bfloat16*)table, out, width, vocab, scale);
     return de_launch(embed_rows_kernel<float>, dim3(n), dim3(threads), 0, s, ids,
-                     (const float*)table, out, width, vocab);
+                     (const float*)table, out, width, vocab, scale);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -615,4 +615,276 @@ DE_EXPORT int de_sample_rows(const float* logits, int rows, int vocab, const flo
     if (rows <= 0) return 0;
     return de_launch(sample_rows_kernel, dim3(rows), dim3(1024), 0, (cudaStream_t)stream, logits,
                      vocab, temperature, seed, position, out);
+}
+
+// ------------------------------------------------------------------------------------------
+// residual sum + layer norm with weight and bias.
+//   x = resid[row] (+ delta[row]);  resid[row] = x (when update)
+//   mean = sum(x) / width;  var = sum((x - mean)^2) / width
+//   out = T((x - mean) * rsqrt(var + eps) * weight + bias)
+// Two passes over the row (first the mean, then the squared deviations from it), all in float32.
+// `rows` as in the RMS norm.  The vector form keeps the row in registers.
+// ------------------------------------------------------------------------------------------
+template <typename T, typename W>
+__global__ void add_layernorm_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                     const W* __restrict__ weight, const W* __restrict__ bias,
+                                     T* __restrict__ out, const int* __restrict__ rows, int width,
+                                     float eps) {
+    __shared__ float scratch[33];
+    const int i_out = blockIdx.x;
+    const int row = rows ? rows[i_out] : i_out;
+    float* r = resid + (size_t)row * width;
+    const T* d = delta ? delta + (size_t)row * width : nullptr;
+    const bool update = (rows == nullptr) && (delta != nullptr);
+    pdl_wait();
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float x = r[i];
+        if (d) x += to_float(d[i]);
+        sum += x;
+    }
+    const float mean = block_sum(sum, scratch) / (float)width;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float x = r[i];
+        if (d) x += to_float(d[i]);
+        ss = fmaf(x - mean, x - mean, ss);
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+    pdl_trigger();
+    T* o = out + (size_t)i_out * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float x = r[i];
+        if (d) x += to_float(d[i]);                  // the same sum as above, bit for bit
+        if (update) r[i] = x;
+        o[i] = from_float<T>(fmaf((x - mean) * inv, to_float(weight[i]), to_float(bias[i])));
+    }
+}
+
+template <typename T, typename W, int CHUNKS>
+__global__ void add_layernorm_vec_kernel(float* __restrict__ resid, const T* __restrict__ delta,
+                                         const W* __restrict__ weight, const W* __restrict__ bias,
+                                         T* __restrict__ out, const int* __restrict__ rows,
+                                         int width, float eps) {
+    __shared__ float scratch[33];
+    const int i_out = blockIdx.x;
+    const int row = rows ? rows[i_out] : i_out;
+    float* r = resid + (size_t)row * width;
+    const T* d = delta ? delta + (size_t)row * width : nullptr;
+    const bool update = (rows == nullptr) && (delta != nullptr);
+    const int quads = width >> 2;
+
+    float wv[CHUNKS][4], bv[CHUNKS][4];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {               // weight and bias are no kernel's output
+        const int qd = threadIdx.x + c * blockDim.x;
+        if (qd < quads) {
+            Vec4<W>::load(weight + 4 * qd, wv[c]);
+            Vec4<W>::load(bias + 4 * qd, bv[c]);
+        }
+    }
+    pdl_wait();
+
+    float x[CHUNKS][4];
+    float sum = 0.0f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int qd = threadIdx.x + c * blockDim.x;
+        if (qd < quads) {
+            Vec4<float>::load(r + 4 * qd, x[c]);
+            if (d) {
+                float dv[4];
+                Vec4<T>::load(d + 4 * qd, dv);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) x[c][e] += dv[e];
+            }
+            if (update) Vec4<float>::store(r + 4 * qd, x[c]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sum += x[c][e];
+        }
+    }
+    const float mean = block_sum(sum, scratch) / (float)width;
+    float ss = 0.0f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int qd = threadIdx.x + c * blockDim.x;
+        if (qd < quads) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                x[c][e] -= mean;
+                ss = fmaf(x[c][e], x[c][e], ss);
+            }
+        }
+    }
+    const float inv = rsqrtf(block_sum(ss, scratch) / (float)width + eps);
+    pdl_trigger();
+    T* o = out + (size_t)i_out * width;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+        const int qd = threadIdx.x + c * blockDim.x;
+        if (qd < quads) {
+            float y[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) y[e] = fmaf(x[c][e] * inv, wv[c][e], bv[c][e]);
+            Vec4<T>::store(o + 4 * qd, y);
+        }
+    }
+}
+
+template <typename T, typename W>
+static int launch_add_layernorm(float* resid, const void* delta, const void* weight,
+                                const void* bias, void* out, const int* rows, int n_out, int width,
+                                float eps, cudaStream_t s) {
+    const bool aligned = width % 4 == 0 && ((uintptr_t)resid % 16 == 0) &&
+                         ((uintptr_t)delta % 8 == 0) && ((uintptr_t)weight % 16 == 0) &&
+                         ((uintptr_t)bias % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const int quads = width / 4;
+#define VEC(CH, TH)                                                                            \
+    return de_launch(add_layernorm_vec_kernel<T, W, CH>, dim3(n_out), dim3(TH), 0, s, resid,   \
+                     (const T*)delta, (const W*)weight, (const W*)bias, (T*)out, rows, width, eps)
+    if (aligned && quads <= 128) VEC(1, 128);
+    if (aligned && quads <= 256) VEC(1, 256);
+    if (aligned && quads <= 512) VEC(2, 256);
+    if (aligned && quads <= 1024) VEC(4, 256);
+    if (aligned && quads <= 2048) VEC(4, 512);
+    if (aligned && quads <= 4096) VEC(8, 512);
+#undef VEC
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    return de_launch(add_layernorm_kernel<T, W>, dim3(n_out), dim3(threads), 0, s, resid,
+                     (const T*)delta, (const W*)weight, (const W*)bias, (T*)out, rows, width, eps);
+}
+
+DE_EXPORT int de_add_layernorm(int dtype, int weight_dtype, float* resid, const void* delta,
+                               const void* weight, const void* bias, void* out, const int* rows,
+                               int n_out, int width, float eps, void* stream) {
+    if (n_out <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16) {
+        if (weight_dtype == DE_BF16)
+            return launch_add_layernorm<__nv_bfloat16, __nv_bfloat16>(resid, delta, weight, bias,
+                                                                      out, rows, n_out, width, eps,
+                                                                      s);
+        return launch_add_layernorm<__nv_bfloat16, float>(resid, delta, weight, bias, out, rows,
+                                                          n_out, width, eps, s);
+    }
+    if (weight_dtype == DE_BF16)
+        return launch_add_layernorm<float, __nv_bfloat16>(resid, delta, weight, bias, out, rows,
+                                                          n_out, width, eps, s);
+    return launch_add_layernorm<float, float>(resid, delta, weight, bias, out, rows, n_out, width,
+                                              eps, s);
+}
+
+// ------------------------------------------------------------------------------------------
+// An activation over a block of columns of a matrix, float32 arithmetic:
+//   kind 0: relu(x)^2     kind 1: tanh(x)     kind 2: silu(x)     kind 3: gelu (tanh form)
+// x [n, cols] with row stride ldx, out [n, cols] with row stride ldo (out may be x).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float activate(float x, int kind) {
+    if (kind == 0) {
+        const float r = fmaxf(x, 0.0f);
+        return r * r;
+    }
+    if (kind == 1) return tanhf(x);
+    if (kind == 2) return x / (1.0f + expf(-x));
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+
+template <typename T>
+__global__ void activation_kernel(const T* __restrict__ x, int ldx, T* __restrict__ out, int ldo,
+                                  int cols, size_t total, int kind) {
+    pdl_wait();
+    pdl_trigger();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / cols;
+        const int i = (int)(idx - n * cols);
+        out[n * ldo + i] = from_float<T>(activate(to_float(x[n * ldx + i]), kind));
+    }
+}
+
+template <typename T>
+__global__ void activation_vec_kernel(const T* __restrict__ x, int ldx, T* __restrict__ out,
+                                      int ldo, int cols, size_t total_quads, int kind) {
+    pdl_wait();
+    pdl_trigger();
+    const int quads = cols >> 2;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_quads;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / quads;
+        const int i = 4 * (int)(idx - n * quads);
+        float v[4];
+        Vec4<T>::load(x + n * ldx + i, v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = activate(v[e], kind);
+        Vec4<T>::store(out + n * ldo + i, v);
+    }
+}
+
+DE_EXPORT int de_activation(int dtype, const void* x, int ldx, void* out, int ldo, int n, int cols,
+                            int kind, void* stream) {
+    if (n <= 0 || cols <= 0) return 0;
+    if (kind < 0 || kind > 3) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    const int piece = dtype == DE_BF16 ? 8 : 16;
+    const bool vec = cols % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)x % piece == 0) &&
+                     ((uintptr_t)out % piece == 0);
+    const size_t total = vec ? (size_t)n * (cols / 4) : (size_t)n * cols;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+#define ACT(T)                                                                                  \
+    do {                                                                                        \
+        if (vec)                                                                                \
+            return de_launch(activation_vec_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, \
+                             s, (const T*)x, ldx, (T*)out, ldo, cols, total, kind);             \
+        return de_launch(activation_kernel<T>, dim3((unsigned)blocks), dim3(threads), 0, s,     \
+                         (const T*)x, ldx, (T*)out, ldo, cols, total, kind);                    \
+    } while (0)
+    if (dtype == DE_BF16) ACT(__nv_bfloat16);
+    ACT(float);
+#undef ACT
+}
+
+// x <- cap * tanh(x / cap) over float32 values (the logits' soft cap).
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap) {
+    pdl_wait();
+    pdl_trigger();
+    const float inv = 1.0f / cap;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        x[idx] = cap * tanhf(x[idx] * inv);
+}
+
+DE_EXPORT int de_softcap(float* x, long long total, float cap, void* stream) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.0f)) return -2;
+    size_t blocks = ((size_t)total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    return de_launch(softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, x,
+                     (size_t)total, cap);
+}
+
+// out = sa * a + sb * b, a and b float32, out of the activation type: two branch outputs joined
+// with fixed weights before they meet the residual stream.
+template <typename T>
+__global__ void scaled_sum_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                  float sa, float sb, T* __restrict__ out, size_t total) {
+    pdl_wait();
+    pdl_trigger();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x)
+        out[idx] = from_float<T>(fmaf(sa, a[idx], sb * b[idx]));
+}
+
+DE_EXPORT int de_scaled_sum(int dtype, const float* a, const float* b, float sa, float sb,
+                            void* out, long long total, void* stream) {
+    if (total <= 0) return 0;
+    size_t blocks = ((size_t)total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        return de_launch(scaled_sum_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s,
+                         a, b, sa, sb, (__nv_bfloat16*)out, (size_t)total);
+    return de_launch(scaled_sum_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, a, b, sa,
+                     sb, (float*)out, (size_t)total);
 }

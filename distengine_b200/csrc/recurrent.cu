@@ -6,6 +6,9 @@
 //   delta rule, per head, S [dk, dv]:   S <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);
 //                                       S <- S + k_t u^T;  o_t = S^T q_t
 //   retention, per head:                S <- decay S + k_t v_t^T;  o_t = S^T q_t
+//   generalized delta rule, per head:   S <- diag(w_t) S - z_t (k_t^T S) + k_t v_t^T;  o_t = S^T r_t
+//                                       (both first terms read the old S; z_t = a_t k_t / (|k_t|^2
+//                                       + 1e-6), which is (a_t u_t) u_t^T S for the unit key u_t)
 //
 // The columns of S never meet: column j needs k_t, q_t, g_t, beta_t and v_t[j] only.  The scan
 // kernel therefore gives a column to four adjacent lanes (each holds a quarter of its rows in
@@ -152,6 +155,60 @@ __global__ void retention_prep_kernel(const T* __restrict__ proj, int ld,
 }
 
 // ------------------------------------------------------------------------------------------
+// Before the generalized delta rule: one block a token.
+//   proj row holds r, k, a (each H dk wide) from columns r_col, k_col, a_col on;
+//   wl float32 [N, H dk]: the low-rank decay projection's output
+//   rr = r, kk = k as float32;  w = exp(-exp(-1/2) * sigmoid(wl + w0))
+//   z  = sigmoid(a + a_bias) * k / (sum over the head of k^2 + 1e-6)
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void gdelta_prep_kernel(const T* __restrict__ proj, int ld, int r_col, int k_col,
+                                   int a_col, const float* __restrict__ wl,
+                                   const float* __restrict__ w0, const float* __restrict__ a_bias,
+                                   float* __restrict__ rr, float* __restrict__ kk,
+                                   float* __restrict__ ww, float* __restrict__ zz, int H, int dk) {
+    const int n = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const T* row = proj + (size_t)n * ld;
+    const size_t base = (size_t)n * (H * dk);
+    const float rate = 0.6065306597126334f;          // exp(-1/2)
+    pdl_wait();
+    for (int h = warp; h < H; h += warps) {
+        const T* ks = row + k_col + h * dk;
+        float ss = 0.0f;
+        for (int i = lane; i < dk; i += 32) {
+            const float x = to_float(ks[i]);
+            ss = fmaf(x, x, ss);
+        }
+        const float inv2 = 1.0f / (warp_sum(ss) + 1e-6f);
+        for (int i = lane; i < dk; i += 32) {
+            const int c = h * dk + i;
+            const float x = to_float(ks[i]);
+            kk[base + c] = x;
+            rr[base + c] = to_float(row[r_col + c]);
+            zz[base + c] = sigmoid_f(to_float(row[a_col + c]) + a_bias[c]) * x * inv2;
+            ww[base + c] = expf(-rate * sigmoid_f(wl[base + c] + w0[c]));
+        }
+    }
+    pdl_trigger();
+}
+
+// silu of `cols` columns of proj into float32 [N, cols] (queries and keys of a mixer without any
+// other preparation).
+template <typename T>
+__global__ void silu_rows_kernel(const T* __restrict__ proj, int ld, float* __restrict__ out,
+                                 int cols, size_t total) {
+    pdl_wait();
+    pdl_trigger();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / cols;
+        const int i = (int)(idx - n * cols);
+        out[idx] = silu_f(to_float(proj[n * ld + i]));
+    }
+}
+
+// ------------------------------------------------------------------------------------------
 // The scan.  grid (sequences, heads, column blocks of COLS); a column belongs to LANES = 4
 // adjacent lanes; thread = LANES * column + share.
 // Rows of the state go to the shares four at a time: row i belongs to share (i / 4) % LANES,
@@ -187,17 +244,20 @@ __device__ __forceinline__ int state_row(int r, int l) {      // register r of s
     return (r >> 2) * (4 * LANES) + (l << 2) + (r & 3);
 }
 
-template <typename VT, int R, bool DELTA, int COLS, int LANES>
+// MODE 0: retention; 1: the delta rule (g, beta); 2: the generalized delta rule (g = w, z).
+template <typename VT, int R, int MODE, int COLS, int LANES>
 __global__ void __launch_bounds__(COLS * LANES)
 scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
             const VT* __restrict__ v, int ldv, const float* __restrict__ g, int ldg,
-            const float* __restrict__ beta, int ldb, const float* __restrict__ decay,
+            const float* __restrict__ beta, int ldb, const float* __restrict__ z, int ldz,
+            const float* __restrict__ decay,
             float* __restrict__ state, long long slot_stride, float* __restrict__ out,
             const int* __restrict__ seq_slot, const int* __restrict__ seq_qstart,
             const int* __restrict__ seq_qlen, int H, int rep, int dk, int dv, int vec16,
             ConvKeep keep) {
     constexpr int PD = LANES * (R + 4);                  // a token's vector in shared memory
-    constexpr int VECS = DELTA ? 3 : 2;              // q, k (, g)
+    constexpr bool DELTA = MODE == 1;
+    constexpr int VECS = MODE == 0 ? 2 : (MODE == 1 ? 3 : 4);      // q, k (, g (, z))
     extern __shared__ __align__(16) float buf[];     // [2][TB][VECS][PD]
     const int s = blockIdx.x, h = blockIdx.y;
     const int col = blockIdx.z * COLS + threadIdx.x / LANES, l = threadIdx.x % LANES;
@@ -234,7 +294,7 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
         const int i = state_row<LANES>(r, l);
         S[r] = (live && i < dk) ? S_g[(size_t)i * dv + col] : 0.0f;
     }
-    const float dec = DELTA ? 0.0f : decay[h];
+    const float dec = MODE == 0 ? decay[h] : 0.0f;
 
     auto issue = [&](int b) {
         float* dst = buf + (size_t)(b & 1) * TB * VECS * PD;
@@ -247,7 +307,8 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
                 float* d = dst + (size_t)t * VECS * PD + (c % LANES) * (R + 4) + ((c / LANES) << 2);
                 cp_async16(d, q + tok * ldq + hk * dk + 4 * c);
                 cp_async16(d + PD, k + tok * ldk + hk * dk + 4 * c);
-                if (DELTA) cp_async16(d + 2 * PD, g + tok * ldg + h * dk + 4 * c);
+                if (MODE >= 1) cp_async16(d + 2 * PD, g + tok * ldg + h * dk + 4 * c);
+                if (MODE == 2) cp_async16(d + 3 * PD, z + tok * ldz + h * dk + 4 * c);
             }
         } else {
             for (int idx = threadIdx.x; idx < count * dk; idx += COLS * LANES) {
@@ -257,7 +318,8 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
                            (((i >> 2) / LANES) << 2) + (i & 3);
                 cp_async4(d, q + tok * ldq + hk * dk + i);
                 cp_async4(d + PD, k + tok * ldk + hk * dk + i);
-                if (DELTA) cp_async4(d + 2 * PD, g + tok * ldg + h * dk + i);
+                if (MODE >= 1) cp_async4(d + 2 * PD, g + tok * ldg + h * dk + i);
+                if (MODE == 2) cp_async4(d + 3 * PD, z + tok * ldz + h * dk + i);
             }
         }
         cp_async_commit();
@@ -306,6 +368,50 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
             // so D^T k, D^T q and k . q are summed together (three sums over the quarter's rows,
             // one butterfly over the four quarters for all three) and the update of S is the
             // last thing a token does, off the next token's critical path but for S itself.
+            if (MODE == 2) {
+                // With p = k^T S (old state) the new state is diag(w) S - z p + k v and the
+                // read-out (w S)^T r - p (z . r) + v (k . r): four sums in one pass over the
+                // quarter's rows, one butterfly for all four, the update of S last.
+                const float4* w4 =
+                    reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD + 2 * PD);
+                const float4* z4 =
+                    reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD + 3 * PD);
+                float pa = 0.0f, pb = 0.0f, oa = 0.0f, ob = 0.0f, za = 0.0f, zb = 0.0f, ka = 0.0f,
+                      kb = 0.0f;
+#pragma unroll
+                for (int r = 0; r < R / 4; ++r) {
+                    const float4 ww = w4[r], kk = k4[r], qq = q4[r], zz = z4[r];
+                    pa = fmaf(S[4 * r + 0], kk.x, pa); S[4 * r + 0] *= ww.x; oa = fmaf(S[4 * r + 0], qq.x, oa);
+                    pb = fmaf(S[4 * r + 1], kk.y, pb); S[4 * r + 1] *= ww.y; ob = fmaf(S[4 * r + 1], qq.y, ob);
+                    pa = fmaf(S[4 * r + 2], kk.z, pa); S[4 * r + 2] *= ww.z; oa = fmaf(S[4 * r + 2], qq.z, oa);
+                    pb = fmaf(S[4 * r + 3], kk.w, pb); S[4 * r + 3] *= ww.w; ob = fmaf(S[4 * r + 3], qq.w, ob);
+                    za = fmaf(zz.x, qq.x, za); ka = fmaf(kk.x, qq.x, ka);
+                    zb = fmaf(zz.y, qq.y, zb); kb = fmaf(kk.y, qq.y, kb);
+                    za = fmaf(zz.z, qq.z, za); ka = fmaf(kk.z, qq.z, ka);
+                    zb = fmaf(zz.w, qq.w, zb); kb = fmaf(kk.w, qq.w, kb);
+                }
+                float p = pa + pb, o = oa + ob, zr = za + zb, kr = ka + kb;
+#pragma unroll
+                for (int step = 1; step < LANES; step <<= 1) {
+                    p += __shfl_xor_sync(0xffffffffu, p, step);
+                    o += __shfl_xor_sync(0xffffffffu, o, step);
+                    zr += __shfl_xor_sync(0xffffffffu, zr, step);
+                    kr += __shfl_xor_sync(0xffffffffu, kr, step);
+                }
+                const float val = vt[t];
+                o = fmaf(val, kr, fmaf(-p, zr, o));
+#pragma unroll
+                for (int r = 0; r < R / 4; ++r) {
+                    const float4 kk = k4[r], zz = z4[r];
+                    S[4 * r + 0] = fmaf(kk.x, val, fmaf(-zz.x, p, S[4 * r + 0]));
+                    S[4 * r + 1] = fmaf(kk.y, val, fmaf(-zz.y, p, S[4 * r + 1]));
+                    S[4 * r + 2] = fmaf(kk.z, val, fmaf(-zz.z, p, S[4 * r + 2]));
+                    S[4 * r + 3] = fmaf(kk.w, val, fmaf(-zz.w, p, S[4 * r + 3]));
+                }
+                if (live && l == 0)
+                    out[(size_t)(tok0 + b * TB + t) * (H * dv) + h * dv + col] = o;
+                continue;
+            }
             float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
             float c0 = 0.0f, c1 = 0.0f, c2 = 0.0f, c3 = 0.0f;      // k . q
             float u;
@@ -374,6 +480,8 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
 // After the scan: every head's output over its root mean square, gated.  A warp a (token, head).
 //   mode 0: out = o / rms * weight[j] * sigmoid(gate)   gate float32 [N, H dv]
 //   mode 1: out = o / rms * silu(gate)                  gate of type T, row stride ld_gate
+//   mode 2: out = o / rms * weight[h dv + j] * sigmoid(gate)   gate of type T; the weight spans
+//           all heads (with H = 1 the root mean square is that of the whole row)
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void head_gate_kernel(const float* __restrict__ o, const void* __restrict__ gate,
@@ -396,9 +504,12 @@ __global__ void head_gate_kernel(const float* __restrict__ o, const void* __rest
         if (mode == 0) {
             const float gt = ((const float*)gate)[(size_t)n * ld_gate + h * dv + j];
             y = y * weight[j] * sigmoid_f(gt);
-        } else {
+        } else if (mode == 1) {
             const float gt = to_float(((const T*)gate)[(size_t)n * ld_gate + h * dv + j]);
             y = y * silu_f(gt);
+        } else {
+            const float gt = to_float(((const T*)gate)[(size_t)n * ld_gate + h * dv + j]);
+            y = y * weight[h * dv + j] * sigmoid_f(gt);
         }
         dst[j] = from_float<T>(y);
     }
@@ -428,23 +539,23 @@ __global__ void mean_of_normed_kernel(const T* __restrict__ a, const T* __restri
     }
 }
 
-template <typename VT, bool DELTA, int COLS, int LANES>
+template <typename VT, int MODE, int COLS, int LANES>
 int launch_scan_cols(int R, dim3 grid, cudaStream_t s, const float* q, int ldq, const float* k,
                      int ldk, const VT* v, int ldv, const float* g, int ldg, const float* beta,
-                     int ldb, const float* decay, float* state, long long slot_stride, float* out,
+                     int ldb, const float* z, int ldz, const float* decay, float* state, long long slot_stride, float* out,
                      const int* seq_slot, const int* seq_qstart, const int* seq_qlen, int H,
                      int rep, int dk, int dv, int vec16, ConvKeep keep) {
 #define SCAN(RR)                                                                                \
     do {                                                                                        \
-        const size_t smem = (size_t)2 * TB * (DELTA ? 3 : 2) * LANES * (RR + 4) * sizeof(float); \
+        const size_t smem = (size_t)2 * TB * (MODE + 2) * LANES * (RR + 4) * sizeof(float);     \
         if (smem > 48 * 1024) {                                                                 \
-            cudaError_t e = cudaFuncSetAttribute(scan_kernel<VT, RR, DELTA, COLS, LANES>,       \
+            cudaError_t e = cudaFuncSetAttribute(scan_kernel<VT, RR, MODE, COLS, LANES>,        \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                                  (int)smem);                                    \
             if (e != cudaSuccess) return (int)e;                                                \
         }                                                                                       \
-        return de_launch(scan_kernel<VT, RR, DELTA, COLS, LANES>, grid, dim3(COLS * LANES),     \
-                         smem, s, q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, decay, state,      \
+        return de_launch(scan_kernel<VT, RR, MODE, COLS, LANES>, grid, dim3(COLS * LANES),      \
+                         smem, s, q, ldq, k, ldk, v, ldv, g, ldg, beta, ldb, z, ldz, decay, state, \
                          slot_stride, out, seq_slot, seq_qstart, seq_qlen, H, rep, dk, dv,      \
                          vec16, keep);                                                          \
     } while (0)
@@ -467,19 +578,21 @@ int sm_count() {
     return count;
 }
 
-template <typename VT, bool DELTA>
+template <typename VT, int MODE>
 int launch_scan(cudaStream_t s, const float* q, int ldq, const float* k, int ldk, const VT* v,
-                int ldv, const float* g, int ldg, const float* beta, int ldb, const float* decay,
+                int ldv, const float* g, int ldg, const float* beta, int ldb, const float* z,
+                int ldz, const float* decay,
                 float* state, long long slot_stride, float* out, const int* seq_slot,
                 const int* seq_qstart, const int* seq_qlen, int n_seqs, int H, int rep, int dk,
                 int dv, ConvKeep keep) {
-    const int vec16 = (dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && (!DELTA || ldg % 4 == 0) &&
+    const int vec16 = (dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && (MODE == 0 || ldg % 4 == 0) &&
                        (uintptr_t)q % 16 == 0 && (uintptr_t)k % 16 == 0 &&
-                       (!DELTA || (uintptr_t)g % 16 == 0)) ? 1 : 0;
+                       (MODE == 0 || (uintptr_t)g % 16 == 0) &&
+                       (MODE != 2 || (ldz % 4 == 0 && (uintptr_t)z % 16 == 0))) ? 1 : 0;
     const long long pairs = (long long)n_seqs * H;
 #define COLS_CASE(CC, LL)                                                                       \
-    return launch_scan_cols<VT, DELTA, CC, LL>(R, grid, s, q, ldq, k, ldk, v, ldv, g, ldg,      \
-                                               beta, ldb, decay, state, slot_stride, out,      \
+    return launch_scan_cols<VT, MODE, CC, LL>(R, grid, s, q, ldq, k, ldk, v, ldv, g, ldg,       \
+                                               beta, ldb, z, ldz, decay, state, slot_stride, out, \
                                                seq_slot, seq_qstart, seq_qlen, H, rep, dk, dv, \
                                                vec16, keep)
     // (eight lanes a column - twice the warps, half the instructions a token and warp - was
@@ -564,35 +677,68 @@ DE_EXPORT int de_retention_prep(int dtype, const void* proj, int ld, const int* 
 }
 
 // v_dtype: the type of v (DE_F32 for the delta rule, whose values come from its own preparation).
-// delta 1: g [N, ldg] and beta [N, ldb] are used; 0: decay [H].  conv_taps > 1: the slots also
-// keep the last conv_taps - 1 rows of the first conv_channels columns of conv_proj (of type
-// conv_dtype, row stride conv_ld) at conv_offset of their state row.
-DE_EXPORT int de_state_scan(int delta, int v_dtype, const float* q, int ldq, const float* k,
+// mode 1: g [N, ldg] and beta [N, ldb] are used (the delta rule); 2: g (the decays w) and z
+// [N, ldz] (the generalized delta rule); 0: decay [H].  conv_taps > 1: the slots also keep the
+// last conv_taps - 1 rows of the first conv_channels columns of conv_proj (of type conv_dtype,
+// row stride conv_ld) at conv_offset of their state row.
+DE_EXPORT int de_state_scan(int mode, int v_dtype, const float* q, int ldq, const float* k,
                             int ldk, const void* v, int ldv, const float* g, int ldg,
-                            const float* beta, int ldb, const float* decay, float* state,
-                            long long slot_stride, float* out, const int* seq_slot,
-                            const int* seq_qstart, const int* seq_qlen, int n_seqs, int H, int rep,
-                            int dk, int dv, const void* conv_proj, int conv_ld, int conv_dtype,
-                            int conv_offset, int conv_channels, int conv_taps, void* stream) {
+                            const float* beta, int ldb, const float* z, int ldz,
+                            const float* decay, float* state, long long slot_stride, float* out,
+                            const int* seq_slot, const int* seq_qstart, const int* seq_qlen,
+                            int n_seqs, int H, int rep, int dk, int dv, const void* conv_proj,
+                            int conv_ld, int conv_dtype, int conv_offset, int conv_channels,
+                            int conv_taps, void* stream) {
     if (n_seqs <= 0) return 0;
     if (dk <= 0 || dk > 256 || dv <= 0 || H <= 0 || rep <= 0 || H % rep) return -2;
+    if (mode < 0 || mode > 2) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     ConvKeep keep = {conv_proj, conv_ld, conv_dtype == DE_BF16 ? 1 : 0, conv_offset,
                      conv_channels, conv_proj ? conv_taps : 0};
-    if (delta) {
+#define SCAN_ARGS(VT)                                                                           \
+    s, q, ldq, k, ldk, (const VT*)v, ldv, g, ldg, beta, ldb, z, ldz, decay, state, slot_stride, \
+        out, seq_slot, seq_qstart, seq_qlen, n_seqs, H, rep, dk, dv, keep
+    if (mode == 1) {
         if (v_dtype != DE_F32) return -4;
-        return launch_scan<float, true>(s, q, ldq, k, ldk, (const float*)v, ldv, g, ldg, beta,
-                                        ldb, decay, state, slot_stride, out, seq_slot, seq_qstart,
-                                        seq_qlen, n_seqs, H, rep, dk, dv, keep);
+        return launch_scan<float, 1>(SCAN_ARGS(float));
     }
-    if (v_dtype == DE_BF16)
-        return launch_scan<__nv_bfloat16, false>(s, q, ldq, k, ldk, (const __nv_bfloat16*)v, ldv,
-                                                 g, ldg, beta, ldb, decay, state, slot_stride, out,
-                                                 seq_slot, seq_qstart, seq_qlen, n_seqs, H, rep,
-                                                 dk, dv, keep);
-    return launch_scan<float, false>(s, q, ldq, k, ldk, (const float*)v, ldv, g, ldg, beta, ldb,
-                                     decay, state, slot_stride, out, seq_slot, seq_qstart,
-                                     seq_qlen, n_seqs, H, rep, dk, dv, keep);
+    if (mode == 2) {
+        if (rep != 1) return -2;
+        if (v_dtype == DE_BF16) return launch_scan<__nv_bfloat16, 2>(SCAN_ARGS(__nv_bfloat16));
+        return launch_scan<float, 2>(SCAN_ARGS(float));
+    }
+    if (v_dtype == DE_BF16) return launch_scan<__nv_bfloat16, 0>(SCAN_ARGS(__nv_bfloat16));
+    return launch_scan<float, 0>(SCAN_ARGS(float));
+#undef SCAN_ARGS
+}
+
+DE_EXPORT int de_gdelta_prep(int dtype, const void* proj, int ld, int r_col, int k_col, int a_col,
+                             const float* wl, const float* w0, const float* a_bias, float* rr,
+                             float* kk, float* ww, float* zz, int n, int H, int dk, void* stream) {
+    if (n <= 0) return 0;
+    if (H <= 0 || dk <= 0) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = n >= 512 ? 128 : (H >= 8 ? 256 : 32 * (H < 1 ? 1 : H));
+    if (dtype == DE_BF16)
+        return de_launch(gdelta_prep_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s,
+                         (const __nv_bfloat16*)proj, ld, r_col, k_col, a_col, wl, w0, a_bias, rr,
+                         kk, ww, zz, H, dk);
+    return de_launch(gdelta_prep_kernel<float>, dim3(n), dim3(threads), 0, s, (const float*)proj,
+                     ld, r_col, k_col, a_col, wl, w0, a_bias, rr, kk, ww, zz, H, dk);
+}
+
+DE_EXPORT int de_silu_rows(int dtype, const void* proj, int ld, float* out, int n, int cols,
+                           void* stream) {
+    if (n <= 0 || cols <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)n * cols;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (dtype == DE_BF16)
+        return de_launch(silu_rows_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s,
+                         (const __nv_bfloat16*)proj, ld, out, cols, total);
+    return de_launch(silu_rows_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s,
+                     (const float*)proj, ld, out, cols, total);
 }
 
 DE_EXPORT int de_head_gate(int dtype, const float* o, const void* gate, int ld_gate,

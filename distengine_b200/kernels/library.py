@@ -23,12 +23,16 @@ P, I, F, L = c_void_p, c_int, c_float, ctypes.c_longlong
 # or a negative number for arguments the kernel refuses)
 SIGNATURES: dict[str, dict[str, list]] = {
     "core": {
-        "de_embed_rows": [I, P, P, P, I, I, I, P],
+        "de_embed_rows": [I, P, P, P, I, I, I, F, P],
         "de_add_rmsnorm": [I, I, P, P, P, P, P, I, I, F, P],
         "de_add_rmsnorm_grouped": [I, I, P, P, P, P, P, I, I, I, F, P],
         "de_rope_kv_write": [I, P, I, P, P, P, I, I, I, I, P, P, P, I, I, I, I, I, P, P],
         "de_silu_mul": [I, P, P, I, I, P],
         "de_sample_rows": [P, I, I, P, P, P, P, P],
+        "de_add_layernorm": [I, I, P, P, P, P, P, P, I, I, F, P],
+        "de_activation": [I, P, I, P, I, I, I, I, P],
+        "de_softcap": [P, L, F, P],
+        "de_scaled_sum": [I, P, P, F, F, P, L, P],
     },
     "gemm_f32": {
         "de_gemm_f32": [P, P, P, I, I, I, I, I, I, P], "de_gemm_f32_small_rows": [],
@@ -66,10 +70,12 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_attn_chunk_rows": [I, I, I, I],
         "de_attn_chunk_decode_ok": [I, I, I, I, I],
         "de_attn_chunk_decode": [I, P, I, P, I, P, P, P, I, I, P, P, P, I, P, P, I, I, I, I, I, F,
-                                 I, P, P],
+                                 I, I, I, F, I, P, P],
+        "de_kv_write_rotated": [I, P, I, P, P, P, I, P, I, I, I, I, P, P, P, I, I, I, I, I, P, P],
+        "de_attn_finish": [I, P, P, P, P, I, P, I, I, I, P],
         "de_kv_write_normed": [I, P, I, I, P, P, I, I, I, F, P, P, P, I, I, I, I, P, P],
         "de_attn_chunk": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, I, F,
-                          I, I, P, P],
+                          I, I, I, F, I, I, P, P],
     },
     "recurrent": {
         "de_recurrent_max_key_dim": [],
@@ -77,8 +83,10 @@ SIGNATURES: dict[str, dict[str, list]] = {
                           I, I, P],
         "de_conv_state": [I, P, I, P, L, I, P, P, P, I, I, I, P],
         "de_retention_prep": [I, P, I, P, P, I, I, I, P, P, I, P],
-        "de_state_scan": [I, I, P, I, P, I, P, I, P, I, P, I, P, P, L, P, P, P, P, I, I, I, I, I,
-                          P, I, I, I, I, I, P],
+        "de_state_scan": [I, I, P, I, P, I, P, I, P, I, P, I, P, I, P, P, L, P, P, P, P, I, I, I,
+                          I, I, P, I, I, I, I, I, P],
+        "de_gdelta_prep": [I, P, I, I, I, I, P, P, P, P, P, P, P, I, I, I, P],
+        "de_silu_rows": [I, P, I, P, I, I, P],
         "de_head_gate": [I, P, P, I, P, P, I, I, I, F, I, P],
         "de_mean_of_normed": [I, P, P, P, P, P, I, I, F, P],
     },

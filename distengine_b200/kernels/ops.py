@@ -75,15 +75,16 @@ def _i32(t: torch.Tensor, name: str) -> None:
 
 
 # ------------------------------------------------------------------------------- embedding
-def embed_rows(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[n] = float32(table[ids[n]]); ids int32 [N], table [V, H], out float32 [N, H]."""
+def embed_rows(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+               scale: float = 1.0) -> None:
+    """out[n] = float32(table[ids[n]]) * scale; ids int32 [N], table [V, H], out float32 [N, H]."""
     _i32(ids, "ids")
     n, (vocab, width) = ids.shape[0], table.shape
     _need(table.is_contiguous() and out.is_contiguous() and out.dtype == torch.float32
           and tuple(out.shape) == (n, width), "embed_rows: out must be float32 [N, H]")
     lib = library.load("core")
     _check(lib.de_embed_rows(_tag(table.dtype), ids.data_ptr(), table.data_ptr(), out.data_ptr(),
-                             n, width, vocab, _stream()), "embed_rows")
+                             n, width, vocab, float(scale), _stream()), "embed_rows")
 
 
 # ------------------------------------------------------------------------------- norm
@@ -115,6 +116,63 @@ def add_rmsnorm(resid: torch.Tensor, delta: "torch.Tensor | None", weight: torch
     _check(lib.de_add_rmsnorm(_tag(out.dtype), _tag(weight.dtype), resid.data_ptr(), _ptr(delta),
                               weight.data_ptr(), out.data_ptr(), _ptr(rows), n_out, width,
                               float(eps), _stream()), "add_rmsnorm")
+
+
+def add_layernorm(resid: torch.Tensor, delta: "torch.Tensor | None", weight: torch.Tensor,
+                  bias: torch.Tensor, eps: float, out: torch.Tensor,
+                  rows: "torch.Tensor | None" = None) -> None:
+    """out = (x - mean(x)) / sqrt(var(x) + eps) * weight + bias with x = resid + delta; resid
+    (float32) takes the sum unless ``rows`` picks the rows to normalise, as in ``add_rmsnorm``."""
+    width = resid.shape[1]
+    n_out = resid.shape[0] if rows is None else rows.shape[0]
+    _need(resid.dtype == torch.float32 and resid.is_contiguous(), "resid must be float32")
+    _need(out.is_contiguous() and tuple(out.shape) == (n_out, width), "add_layernorm: out shape")
+    _need(weight.is_contiguous() and weight.shape == (width,) and bias.is_contiguous()
+          and bias.shape == (width,) and bias.dtype == weight.dtype,
+          "add_layernorm: weight and bias must be [width] of one dtype")
+    if delta is not None:
+        _need(delta.dtype == out.dtype and delta.is_contiguous()
+              and delta.shape == resid.shape, "add_layernorm: delta must match resid's shape and "
+              "the output's dtype")
+    if rows is not None:
+        _i32(rows, "rows")
+    lib = library.load("core")
+    _check(lib.de_add_layernorm(_tag(out.dtype), _tag(weight.dtype), resid.data_ptr(),
+                                _ptr(delta), weight.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                                _ptr(rows), n_out, width, float(eps), _stream()), "add_layernorm")
+
+
+# ------------------------------------------------------------------------------- element-wise
+ACTIVATIONS = {"relu2": 0, "tanh": 1, "silu": 2, "gelu_tanh": 3}
+
+
+def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out = act(x) element by element (float32 arithmetic): ``relu2`` the square of relu,
+    ``tanh``, ``silu``, ``gelu_tanh``.  x and out [N, cols] with free row strides; out may be x."""
+    _need(kind in ACTIVATIONS, f"activation: unknown kind '{kind}'; known: {sorted(ACTIVATIONS)}")
+    _need(x.dim() == 2 and x.shape == out.shape and x.dtype == out.dtype and x.stride(1) == 1
+          and out.stride(1) == 1, "activation: x and out [N, cols] of one dtype")
+    lib = library.load("core")
+    _check(lib.de_activation(_tag(x.dtype), x.data_ptr(), x.stride(0), out.data_ptr(),
+                             out.stride(0), x.shape[0], x.shape[1], ACTIVATIONS[kind], _stream()),
+           "activation")
+
+
+def softcap_(x: torch.Tensor, cap: float) -> None:
+    """x <- cap * tanh(x / cap) in place; x float32, contiguous."""
+    _need(x.dtype == torch.float32 and x.is_contiguous() and cap > 0, "softcap_: float32, cap > 0")
+    lib = library.load("core")
+    _check(lib.de_softcap(x.data_ptr(), x.numel(), float(cap), _stream()), "softcap")
+
+
+def scaled_sum(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float, out: torch.Tensor) -> None:
+    """out = sa * a + sb * b; a, b float32, out of any kernel dtype, all contiguous of one shape."""
+    _need(a.dtype == b.dtype == torch.float32 and a.shape == b.shape == out.shape
+          and a.is_contiguous() and b.is_contiguous() and out.is_contiguous(),
+          "scaled_sum: a, b float32 and out, contiguous and of one shape")
+    lib = library.load("core")
+    _check(lib.de_scaled_sum(_tag(out.dtype), a.data_ptr(), b.data_ptr(), float(sa), float(sb),
+                             out.data_ptr(), out.numel(), _stream()), "scaled_sum")
 
 
 # ------------------------------------------------------------------------------- rotation + cache write

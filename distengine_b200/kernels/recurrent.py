@@ -91,19 +91,23 @@ def retention_prep(proj: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, 
 def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor,
                out: torch.Tensor, heads: int, qk_heads: int, key_dim: int, value_dim: int, ctx,
                g: "torch.Tensor | None" = None, beta: "torch.Tensor | None" = None,
-               decay: "torch.Tensor | None" = None, keep: "tuple | None" = None) -> None:
+               decay: "torch.Tensor | None" = None, keep: "tuple | None" = None,
+               z: "torch.Tensor | None" = None) -> None:
     """Walk every sequence's tokens of the step through its state ``state`` [slots, >= H dk dv]
     (float32, rows [h][key channel][value channel] at the front) and write the read-outs, float32
     [N, H dv].  With ``g`` [N, H dk] and ``beta`` [N, H]: the delta rule with a decay per key
-    channel.  With ``decay`` [H]: retention.  q, k float32 [N, qk_heads dk]; v [N, H dv] in
+    channel.  With ``g`` and ``z`` [N, H dk]: the generalized delta rule, S <- diag(g) S -
+    z (k^T S) + k v^T with both first terms reading the old S.  With ``decay`` [H]: retention.
+    q, k float32 [N, qk_heads dk]; v [N, H dv] in
     float32 or the activation dtype (any row stride).  ``keep`` = (proj, offset, channels, taps):
     the slots also keep, at ``offset`` of their rows, the last ``taps - 1`` rows of the first
     ``channels`` columns of ``proj`` of every sequence (a convolution's inputs, as ``conv_state``
     does; the kernel before this one has read the old ones)."""
     n = q.shape[0]
-    delta = g is not None
-    _need(delta != (decay is not None) and (beta is not None) == delta,
-          "state_scan: give g and beta, or decay")
+    general = z is not None
+    delta = g is not None and not general
+    _need((g is not None) != (decay is not None) and (beta is not None) == delta
+          and (not general or g is not None), "state_scan: give g and beta, g and z, or decay")
     _need(key_dim <= max_key_dim(), f"state_scan: key size {key_dim} is beyond {max_key_dim()}")
     for t, name in ((q, "q"), (k, "k"), (state, "state"), (out, "out")):
         _f32(t, name)
@@ -118,6 +122,10 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
         _f32(g, "g"), _f32(beta, "beta")
         _need(g.shape == (n, heads * key_dim) and beta.shape == (n, heads)
               and v.dtype == torch.float32, "state_scan: g [N, H dk], beta [N, H], v float32")
+    elif general:
+        _f32(g, "g"), _f32(z, "z")
+        _need(g.shape == z.shape == (n, heads * key_dim) and qk_heads == heads,
+              "state_scan: g and z [N, H dk], one query/key head a head")
     else:
         _f32(decay, "decay")
         _need(decay.shape == (heads,) and decay.is_contiguous(), "state_scan: decay [H]")
@@ -129,26 +137,69 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
               "state_scan: the kept convolution inputs do not fit")
         conv = (proj.data_ptr(), proj.stride(0), _tag(proj.dtype), offset, channels, taps)
     lib = library.load("recurrent")
-    _check(lib.de_state_scan(int(delta), _tag(v.dtype), q.data_ptr(), q.stride(0), k.data_ptr(),
-                             k.stride(0), v.data_ptr(), v.stride(0), _ptr(g),
-                             g.stride(0) if delta else 0, _ptr(beta),
-                             beta.stride(0) if delta else 0, _ptr(decay), state.data_ptr(),
+    _check(lib.de_state_scan(2 if general else int(delta), _tag(v.dtype), q.data_ptr(),
+                             q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
+                             _ptr(g), g.stride(0) if g is not None else 0, _ptr(beta),
+                             beta.stride(0) if delta else 0, _ptr(z),
+                             z.stride(0) if general else 0, _ptr(decay), state.data_ptr(),
                              state.stride(0), out.data_ptr(), ctx.seq_slot.data_ptr(),
                              ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, heads,
                              heads // qk_heads, key_dim, value_dim, *conv, _stream()),
            "state_scan")
 
 
+def gdelta_prep(proj: torch.Tensor, r_col: int, k_col: int, a_col: int, wl: torch.Tensor,
+                w0: torch.Tensor, a_bias: torch.Tensor, rr: torch.Tensor, kk: torch.Tensor,
+                ww: torch.Tensor, zz: torch.Tensor, heads: int, key_dim: int) -> None:
+    """What the generalized delta rule needs of every token besides its values, all float32
+    [N, H dk]: r and k as they stand in ``proj`` (from columns ``r_col`` and ``k_col``), the
+    decays w = exp(-exp(-1/2) sigmoid(wl + w0)) from the low-rank projection ``wl`` (float32), and
+    z = sigmoid(a + a_bias) k / (|k|^2 + 1e-6) per head with a from column ``a_col``."""
+    n, hk = proj.shape[0], heads * key_dim
+    _need(proj.stride(1) == 1 and proj.shape[1] >= max(r_col, k_col, a_col) + hk,
+          "gdelta_prep: proj is too narrow")
+    for t, name in ((wl, "wl"), (rr, "rr"), (kk, "kk"), (ww, "ww"), (zz, "zz")):
+        _f32(t, name)
+        _need(tuple(t.shape) == (n, hk) and t.is_contiguous(),
+              f"gdelta_prep: {name} must be contiguous [N, H dk]")
+    for t, name in ((w0, "w0"), (a_bias, "a_bias")):
+        _f32(t, name)
+        _need(tuple(t.shape) == (hk,) and t.is_contiguous(), f"gdelta_prep: {name} [H dk]")
+    lib = library.load("recurrent")
+    _check(lib.de_gdelta_prep(_tag(proj.dtype), proj.data_ptr(), proj.stride(0), r_col, k_col,
+                              a_col, wl.data_ptr(), w0.data_ptr(), a_bias.data_ptr(),
+                              rr.data_ptr(), kk.data_ptr(), ww.data_ptr(), zz.data_ptr(), n, heads,
+                              key_dim, _stream()), "gdelta_prep")
+
+
+def silu_rows(proj: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(proj) as float32; proj [N, cols] with a free row stride, out contiguous."""
+    _f32(out, "out")
+    _need(proj.dim() == 2 and proj.stride(1) == 1 and out.is_contiguous()
+          and out.shape == proj.shape, "silu_rows: proj [N, cols], out contiguous of that shape")
+    lib = library.load("recurrent")
+    _check(lib.de_silu_rows(_tag(proj.dtype), proj.data_ptr(), proj.stride(0), out.data_ptr(),
+                            proj.shape[0], proj.shape[1], _stream()), "silu_rows")
+
+
 def head_gate(o: torch.Tensor, gate: torch.Tensor, weight: "torch.Tensor | None",
-              out: torch.Tensor, heads: int, value_dim: int, eps: float) -> None:
+              out: torch.Tensor, heads: int, value_dim: int, eps: float,
+              spanning: bool = False) -> None:
     """out = o / rms(o over each head) * weight * sigmoid(gate) with a float32 ``gate`` and a
-    ``weight`` [dv]; or, without a weight, o / rms * silu(gate) with a gate of out's dtype."""
+    ``weight`` [dv]; or, without a weight, o / rms * silu(gate) with a gate of out's dtype; or
+    (``spanning``) o / rms * weight * sigmoid(gate) with a ``weight`` [H dv] that spans the heads
+    and a gate of out's dtype (``heads`` 1 and ``value_dim`` the whole row: the root mean square
+    is the row's)."""
     n = o.shape[0]
     _f32(o, "o")
     _need(o.is_contiguous() and o.shape == (n, heads * value_dim) and out.is_contiguous()
           and out.shape == o.shape and gate.stride(1) == 1 and gate.shape == o.shape,
           "head_gate: o, gate and out must be [N, H dv]")
-    if weight is not None:
+    if spanning:
+        _f32(weight, "weight")
+        _need(weight.shape == (heads * value_dim,) and gate.dtype == out.dtype,
+              "head_gate: a spanning weight is [H dv] and its gate has the output's dtype")
+    elif weight is not None:
         _f32(weight, "weight"), _f32(gate, "gate")
         _need(weight.shape == (value_dim,), "head_gate: weight [dv]")
     else:
@@ -156,7 +207,8 @@ def head_gate(o: torch.Tensor, gate: torch.Tensor, weight: "torch.Tensor | None"
     lib = library.load("recurrent")
     _check(lib.de_head_gate(_tag(out.dtype), o.data_ptr(), gate.data_ptr(), gate.stride(0),
                             _ptr(weight), out.data_ptr(), n, heads, value_dim, float(eps),
-                            0 if weight is not None else 1, _stream()), "head_gate")
+                            2 if spanning else (0 if weight is not None else 1), _stream()),
+           "head_gate")
 
 
 def mean_of_normed(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor,
@@ -175,6 +227,13 @@ def mean_of_normed(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch
 
 
 # ------------------------------------------------------------------------------- chunk attention
+def _penalty(r1, r2, heads: int) -> None:
+    _need((r1 is None) == (r2 is None), "attention: r1 and r2 come together")
+    if r1 is not None:
+        _f32(r1, "r1"), _f32(r2, "r2")
+        _need(r1.shape == r2.shape == (heads,), "attention: r1, r2 [heads]")
+
+
 def chunk_rows_per_tile(dtype: torch.dtype, key_dim: int, value_dim: int, wide: bool) -> int:
     """Rows of a tile of the chunk attention: 8, or 32 for steps with prompt portions (``wide``)
     at sizes whose rows are whole 16-byte pieces."""
@@ -192,24 +251,27 @@ def chunk_decode_ok(dtype: torch.dtype, heads: int, kv_heads: int, key_dim: int,
 def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
                            v_pages: torch.Tensor, block_table: torch.Tensor, r1: torch.Tensor,
                            r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
-                           value_dim: int, scale: float, chunk: int, ctx) -> None:
+                           value_dim: int, scale: float, chunk: int, ctx, window: int = 0,
+                           keep_first: int = 0, softcap: float = 0.0) -> None:
     """``chunk_attention`` for a step in which every sequence brings one token: a block a
     (sequence, kv head), its warps share the key tiles out; no work items."""
-    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == k_pages.dtype
+          and out.dtype in (q.dtype, torch.float32)
           and out.shape[1] == heads * value_dim and q.shape[0] == ctx.n_seqs,
           "chunk_attention_decode: q, out and pages; one token a sequence")
     _i32(block_table, "block_table")
-    _f32(r1, "r1"), _f32(r2, "r2")
-    _need(r1.shape == r2.shape == (heads,), "chunk_attention_decode: r1, r2 [heads]")
+    _penalty(r1, r2, heads)
     lib = library.load("attention_chunk")
     _check(lib.de_attn_chunk_decode(_tag(q.dtype), q.data_ptr(), q.stride(0), out.data_ptr(),
                                     out.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
                                     block_table.data_ptr(), block_table.stride(0),
                                     k_pages.shape[0], ctx.seq_slot.data_ptr(),
                                     ctx.seq_qstart.data_ptr(), ctx.seq_pos0.data_ptr(),
-                                    ctx.n_seqs, r1.data_ptr(), r2.data_ptr(), heads, kv_heads,
+                                    ctx.n_seqs, _ptr(r1), _ptr(r2), heads, kv_heads,
                                     key_dim, value_dim, k_pages.shape[2], float(scale),
-                                    int(chunk), ctx.status.data_ptr(), _stream()),
+                                    int(chunk), int(window), int(keep_first), float(softcap),
+                                    int(out.dtype == torch.float32 and q.dtype != torch.float32),
+                                    ctx.status.data_ptr(), _stream()),
            "chunk_attention_decode")
 
 
@@ -238,21 +300,80 @@ def kv_write_normed(proj: torch.Tensor, k_col: int, kv_heads: int, key_dim: int,
 def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
                     v_pages: torch.Tensor, block_table: torch.Tensor, items: torch.Tensor,
                     r1: torch.Tensor, r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
-                    value_dim: int, scale: float, chunk: int, ctx, tile_rows: int = 8) -> None:
+                    value_dim: int, scale: float, chunk: int, ctx, tile_rows: int = 8,
+                    window: int = 0, keep_first: int = 0, softcap: float = 0.0) -> None:
     """Attention of the step's rows over the pages: q rows of [heads dk] at the front of ``q``
     (row stride free), out [N, heads dv]; ``tile_rows``: the rows of a tile that ``items`` were
     cut for (``chunk_rows_per_tile``); see ``csrc/attention_chunk.cu``."""
-    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == k_pages.dtype
+    _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == k_pages.dtype
+          and out.dtype in (q.dtype, torch.float32)
           and out.shape[1] == heads * value_dim, "chunk_attention: q, out and pages")
     _i32(block_table, "block_table"), _i32(items, "items")
-    _f32(r1, "r1"), _f32(r2, "r2")
-    _need(r1.shape == r2.shape == (heads,), "chunk_attention: r1, r2 [heads]")
+    _penalty(r1, r2, heads)
     lib = library.load("attention_chunk")
     _check(lib.de_attn_chunk(_tag(q.dtype), q.data_ptr(), q.stride(0), out.data_ptr(),
                              out.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
                              block_table.data_ptr(), block_table.stride(0), k_pages.shape[0],
                              ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(),
                              ctx.seq_qlen.data_ptr(), ctx.seq_pos0.data_ptr(), items.data_ptr(),
-                             items.shape[0], r1.data_ptr(), r2.data_ptr(), heads, kv_heads,
+                             items.shape[0], _ptr(r1), _ptr(r2), heads, kv_heads,
                              key_dim, value_dim, k_pages.shape[2], float(scale), int(chunk),
+                             int(window), int(keep_first), float(softcap),
+                             int(out.dtype == torch.float32 and q.dtype != torch.float32),
                              int(tile_rows), ctx.status.data_ptr(), _stream()), "chunk_attention")
+
+
+def kv_write_rotated(proj: torch.Tensor, fk: torch.Tensor, rotary_dim: int,
+                     fv: "torch.Tensor | None", heads: int, kv_heads: int, key_dim: int,
+                     value_dim: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     block_table: torch.Tensor, write_kv: bool, ctx) -> None:
+    """Turn the queries at the front of ``proj`` ([q (H dk) | k (G dk) | v (G dv) | ...]) by their
+    tokens' positions in place and store the turned keys and the values in the pages; ``fk``
+    [rotary_dim / 2] are the frequencies of the first ``rotary_dim`` features of queries and
+    keys, ``fv`` [dv / 2] (or None: values as they are) those of all features of the values.
+    ``write_kv`` false: a run that reads another run's cache turns its queries only."""
+    need = heads * key_dim + (kv_heads * (key_dim + value_dim) if write_kv else 0)
+    _need(proj.stride(1) == 1 and proj.shape[1] >= need and proj.dtype == k_pages.dtype
+          == v_pages.dtype, "kv_write_rotated: proj and pages")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+          and tuple(k_pages.shape[1:]) == (kv_heads, k_pages.shape[2], key_dim)
+          and tuple(v_pages.shape) == (*k_pages.shape[:3], value_dim),
+          "kv_write_rotated: pages must be [pages, kv_heads, page, dk] and [..., dv]")
+    _i32(block_table, "block_table")
+    _f32(fk, "fk")
+    _need(rotary_dim % 2 == 0 and 0 <= rotary_dim <= key_dim and fk.shape == (rotary_dim // 2,),
+          "kv_write_rotated: fk [rotary_dim / 2], rotary_dim even and at most the key size")
+    if fv is not None:
+        _f32(fv, "fv")
+        _need(value_dim % 2 == 0 and fv.shape == (value_dim // 2,),
+              "kv_write_rotated: fv [dv / 2], dv even")
+    lib = library.load("attention_chunk")
+    _check(lib.de_kv_write_rotated(_tag(proj.dtype), proj.data_ptr(), proj.stride(0),
+                                   ctx.positions.data_ptr(), ctx.token_slot.data_ptr(),
+                                   fk.data_ptr(), rotary_dim, _ptr(fv), heads, kv_heads, key_dim,
+                                   value_dim, k_pages.data_ptr(), v_pages.data_ptr(),
+                                   block_table.data_ptr(), block_table.stride(0),
+                                   k_pages.shape[2], k_pages.shape[0], int(write_kv),
+                                   proj.shape[0], ctx.status.data_ptr(), _stream()),
+           "kv_write_rotated")
+
+
+def attention_finish(o: torch.Tensor, fv: "torch.Tensor | None", gate: "torch.Tensor | None",
+                     out: torch.Tensor, heads: int, value_dim: int, ctx) -> None:
+    """out = the heads' results ``o`` (float32 [N, H dv]) turned back by their tokens' positions
+    (``fv`` as in ``kv_write_rotated``) and multiplied by sigmoid(``gate``) (of out's dtype, free
+    row stride), where given."""
+    n = o.shape[0]
+    _f32(o, "o")
+    _need(o.is_contiguous() and o.shape == (n, heads * value_dim) and out.is_contiguous()
+          and out.shape == o.shape, "attention_finish: o and out [N, H dv]")
+    if fv is not None:
+        _f32(fv, "fv")
+        _need(value_dim % 2 == 0 and fv.shape == (value_dim // 2,), "attention_finish: fv [dv / 2]")
+    if gate is not None:
+        _need(gate.dtype == out.dtype and gate.stride(1) == 1 and gate.shape == o.shape,
+              "attention_finish: gate [N, H dv] of out's dtype")
+    lib = library.load("attention_chunk")
+    _check(lib.de_attn_finish(_tag(out.dtype), o.data_ptr(), ctx.positions.data_ptr(), _ptr(fv),
+                              _ptr(gate), gate.stride(0) if gate is not None else 0,
+                              out.data_ptr(), n, heads, value_dim, _stream()), "attention_finish")

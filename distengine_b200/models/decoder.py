@@ -131,7 +131,7 @@ class DecoderModel:
         """Run the step's tokens through the plan; logits float32 [R, vocabulary] at
         ``ctx.logit_rows``."""
         resid = ctx.buffer("model.residual", (ctx.n_tokens, self.config.width), torch.float32)
-        ops.embed_rows(ctx.token_ids, self.embedding, resid)
+        ops.embed_rows(ctx.token_ids, self.embedding, resid, self.config.embedding_scale)
         stream = ResidualStream(resid)
         for index, entry in enumerate(self.plan):
             # the norm and mixer that read the stream next, for blocks that hand a norm's work to
@@ -148,6 +148,8 @@ class DecoderModel:
             return logits
         last = self.final_norm.forward(stream, ctx, rows=rows, out_name="model.final_norm")
         ops.linear(last, self.output, out=logits, out_dtype=torch.float32)
+        if self.config.logit_softcap is not None:
+            ops.softcap_(logits, self.config.logit_softcap)
         return logits
 
 

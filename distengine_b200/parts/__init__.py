@@ -1,5 +1,5 @@
 from . import (attention, block, chunk_attention, mlp, norm, parallel,  # noqa: F401
-               recurrent, rope)  # (register the built-in kinds)
+               recurrent, rope, window_attention)  # (register the built-in kinds)
 from .base import (Block, FeedForward, Mixer, Norm, PagedKVSpec, Part, PositionEncoding,
                    StateSpec, build_block, build_feed_forward, build_mixer, build_norm,
                    build_position_encoding, register_block, register_feed_forward,

@@ -29,12 +29,14 @@ class PagedKVSpec:
     ``value_dim``: the values' size where it is not the keys' ([pages, kv_heads, page, value_dim]).
     ``chunk``: a token reads keys of its own chunk of positions only (chunks of this many
     positions, counted from 0), so pages that lie wholly before the chunk of the next position are
-    given back."""
+    given back.  ``keep_first``: with a window, the first this many keys of a sequence stay
+    readable for ever, so the pages that hold them are never given back while the request lives."""
     kv_heads: int
     head_dim: int
     window: int | None = None
     value_dim: int | None = None
     chunk: int | None = None
+    keep_first: int = 0
 
     @property
     def v_dim(self) -> int:

@@ -88,7 +88,7 @@ class ChunkAttention(ProjectedMixer):
         prep.add(name, plan.items)
         prep.notes[self.key] = rows
 
-    def run(self, proj, ctx, cache, ahead=None):
+    def run(self, proj, ctx, cache, ahead=None, out_dtype=None):
         if cache is None or cache.kind != "paged":
             raise ValueError("chunk attention needs a paged key/value cache")
         n = proj.shape[0]
@@ -105,7 +105,7 @@ class ChunkAttention(ProjectedMixer):
                                ctx.arrays[self.key + "/items"], self.r1, self.r2, self.heads,
                                self.kv_heads, self.dk, self.dv, self.scale, self.chunk, ctx,
                                tile_rows=ctx.notes[self.key])
-        return self.project_out(context, "chunk_attention.out", ctx, ahead)
+        return self.project_out(context, "chunk_attention.out", ctx, ahead, out_dtype=out_dtype)
 
 
 register_mixer("chunk_attention", ChunkAttention)

@@ -63,4 +63,38 @@ class GatedMLP(FeedForward):
         return out
 
 
+class DenseMLP(FeedForward):
+    """down( act( up(x) ) ) without a gate; ``activation`` is one of ``ops.ACTIVATIONS`` (the
+    square of relu, tanh, silu, gelu in its tanh form)."""
+
+    def __init__(self, width: int, inner: int, activation: str, dtype: torch.dtype,
+                 device: torch.device, names: "tuple[str, str]" = ("up", "down")) -> None:
+        super().__init__(dtype, device)
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"dense_mlp: activation '{activation}' is not implemented; "
+                             f"{sorted(ops.ACTIVATIONS)} are")
+        self.width, self.inner, self.activation, self.names = width, inner, activation, tuple(names)
+        self.w_up: "torch.Tensor | None" = None
+        self.w_down: "torch.Tensor | None" = None
+
+    def tensors(self):
+        up, down = self.names
+        return {up: ((self.inner, self.width), "matrix"), down: ((self.width, self.inner), "matrix")}
+
+    def load(self, tensors):
+        up, down = self.names
+        self.w_up = compute_matrix(tensors[up], self.dtype, self.device)
+        self.w_down = compute_matrix(tensors[down], self.dtype, self.device)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, ahead=None) -> torch.Tensor:
+        n = x.shape[0]
+        act = ctx.buffer("mlp.act", (n, self.inner))
+        ops.linear(x, self.w_up, out=act, status=ctx.status)
+        ops.activation(act, act, self.activation)
+        out = ctx.buffer("mlp.out", (n, self.width))
+        ops.linear(act, self.w_down, out=out, status=ctx.status)
+        return out
+
+
 register_feed_forward("gated_mlp", GatedMLP)
+register_feed_forward("dense_mlp", DenseMLP)

@@ -1,4 +1,4 @@
-"""RMS norm with the residual sum folded in, optionally in groups.
+"""RMS norm with the residual sum folded in, optionally in groups; layer norm with weight and bias.
 
 Formula (src/layers/layernorm.py:12-23): float32 mean of squares, x * rsqrt(mean + eps), cast to
 the activation dtype, then times the weight.  The block's residual sums
@@ -7,6 +7,10 @@ the activation dtype, then times the weight.  The block's residual sums
 ``groups`` > 1: the row is cut into that many equal consecutive parts and each part is divided by
 its own root mean square; the weight still spans the row.  ``tensor``: the local name of the
 weight (architectures differ in it).
+
+``layernorm``: (x - mean) / sqrt(mean of squared deviations + eps) * weight + bias, the statistics
+in float32 over the whole row; ``tensor`` and ``bias`` are the local names of its two vectors.  The
+mean does not commute with a matrix product, so this norm never rides on the products around it.
 """
 
 from __future__ import annotations
@@ -56,4 +60,34 @@ class RMSNorm(Norm):
         return out
 
 
+class LayerNorm(Norm):
+    def __init__(self, width: int, eps: float, dtype: torch.dtype, device: torch.device,
+                 tensor: str = "weight", bias: str = "bias") -> None:
+        super().__init__(dtype, device)
+        self.width, self.eps, self.tensor, self.bias_name = width, eps, tensor, bias
+        self.weight: "torch.Tensor | None" = None
+        self.bias: "torch.Tensor | None" = None
+
+    def tensors(self):
+        return {self.tensor: ((self.width,), "vector"), self.bias_name: ((self.width,), "bias")}
+
+    def load(self, tensors):
+        self.weight = stored_vector(tensors[self.tensor], self.dtype, self.device)
+        self.bias = stored_vector(tensors[self.bias_name], self.dtype, self.device)
+        if self.bias.dtype != self.weight.dtype:
+            self.bias = self.bias.to(self.weight.dtype)
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, rows=None,
+                out_name: str = "norm.out") -> torch.Tensor:
+        if stream.ahead is not None:
+            raise RuntimeError("a layer norm's work cannot be handed to the product before it")
+        n_out = stream.resid.shape[0] if rows is None else rows.shape[0]
+        out = ctx.buffer(out_name, (n_out, self.width))
+        ops.add_layernorm(stream.resid, stream.pending, self.weight, self.bias, self.eps, out, rows)
+        if rows is None:
+            stream.pending = None              # it is part of the residual now
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("layernorm", LayerNorm)

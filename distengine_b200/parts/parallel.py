@@ -1,13 +1,18 @@
-"""Mixers side by side: every branch reads the same input, each branch's output is divided by its
-root mean square over the width and multiplied by a weight of its own, and the results are
-averaged.
+"""Mixers side by side: every branch reads the same input.  ``combine`` says how their outputs
+meet:
 
-    out = ( rms_norm(branch_0(x)) * w_0 + rms_norm(branch_1(x)) * w_1 ) / 2
+* ``mean_of_normed`` (the default): each branch's output is divided by its root mean square over
+  the width and multiplied by a weight of its own (``<name_i>.out``), and the results are averaged,
+
+      out = ( rms_norm(branch_0(x)) * w_0 + rms_norm(branch_1(x)) * w_1 ) / 2
+
+* ``weighted_sum``: out = scales[0] * branch_0(x) + scales[1] * branch_1(x) with fixed numbers; the
+  branches' outputs stay float32 until they are summed.
 
 The branches are projected mixers (``parts.recurrent.ProjectedMixer``): their input matrices are
 stacked, so the layer's input goes through one product for all of them.  The mixer's cache spec is
 the tuple of its branches' specs; its run gets one binding per branch.  Branch i's tensors live
-under ``<name_i>.`` and its weight is ``<name_i>.out``.
+under ``<name_i>.``.
 """
 
 from __future__ import annotations
@@ -24,12 +29,17 @@ from .recurrent import ProjectedMixer, stack_segments, vector32
 
 class ParallelMixer(Mixer):
     def __init__(self, width: int, eps: float, branches, dtype: torch.dtype,
-                 device: torch.device) -> None:
+                 device: torch.device, combine: str = "mean_of_normed", scales=None) -> None:
         """``branches``: ((name, PartSpec), (name, PartSpec))."""
         super().__init__(dtype, device)
         if len(branches) != 2:
             raise ValueError("parallel: two branches side by side are implemented")
-        self.width, self.eps = width, eps
+        if combine not in ("mean_of_normed", "weighted_sum"):
+            raise ValueError(f"parallel: combine '{combine}' is not implemented")
+        if combine == "weighted_sum" and (scales is None or len(scales) != 2):
+            raise ValueError("parallel: a weighted sum needs one scale for each branch")
+        self.width, self.eps, self.combine = width, eps, combine
+        self.scales = None if scales is None else tuple(float(x) for x in scales)
         self.names = [name for name, _ in branches]
         self.branches = [build_mixer(spec, dtype, device) for _, spec in branches]
         for branch in self.branches:
@@ -44,7 +54,8 @@ class ParallelMixer(Mixer):
         for name, branch in zip(self.names, self.branches):
             for local, what in branch.tensors().items():
                 out[f"{name}.{local}"] = what
-            out[f"{name}.out"] = ((self.width,), "vector")
+            if self.combine == "mean_of_normed":
+                out[f"{name}.out"] = ((self.width,), "vector")
         return out
 
     def load(self, tensors):
@@ -57,7 +68,9 @@ class ParallelMixer(Mixer):
         self.w_in = compute_matrix(stacked, self.dtype, self.device)
         for branch in self.branches:
             branch.finish_load()
-        self.out_weights = [vector32(tensors[f"{name}.out"], self.device) for name in self.names]
+        if self.combine == "mean_of_normed":
+            self.out_weights = [vector32(tensors[f"{name}.out"], self.device)
+                                for name in self.names]
 
     def cache_spec(self):
         return tuple(branch.cache_spec() for branch in self.branches)
@@ -81,10 +94,16 @@ class ParallelMixer(Mixer):
         n = x.shape[0]
         proj = ctx.buffer("parallel.proj", (n, self.w_in.shape[0]))
         ops.linear(x, self.w_in, out=proj, status=ctx.status, before=before)
+        out = ctx.buffer("parallel.out", (n, self.width))
+        if self.combine == "weighted_sum":
+            outs = [branch.run(proj[:, at: at + rows], ctx, binding, out_dtype=torch.float32)
+                    for branch, at, rows, binding in zip(self.branches, self.offsets, self.rows,
+                                                         cache.parts)]
+            ops.scaled_sum(outs[0], outs[1], self.scales[0], self.scales[1], out)
+            return out
         outs = [branch.run(proj[:, at: at + rows], ctx, binding)
                 for branch, at, rows, binding in zip(self.branches, self.offsets, self.rows,
                                                      cache.parts)]
-        out = ctx.buffer("parallel.out", (n, self.width))
         rk.mean_of_normed(outs[0], outs[1], self.out_weights[0], self.out_weights[1], out,
                           self.eps)
         return out

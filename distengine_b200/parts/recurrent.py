@@ -23,6 +23,20 @@ Retention, per head with state S [dk, dv]:
     S <- decay[h] S + k v^T;  o = S^T q
     out       = W_o [ o / rms(o) * silu(W_g x) ]
 
+Generalized delta rule, per head with state S [dk, dv] and the unit key u = k / sqrt(|k|^2 + 1e-6):
+
+    r, k, v   = W_r x, W_k x, W_v x
+    w         = exp(-exp(-1/2) * sigmoid(W_w2 tanh(W_w1 x) + w0))     decay per head and key channel
+    a         = sigmoid(W_a x + a_bias)                               removal rate, likewise
+    S <- diag(w) S - (a u) (u^T S) + k v^T      (both first terms read the old S);  o = S^T r
+    out       = W_o [ o / rms(o) * norm * sigmoid(W_g x) ]            rms per head, norm [H dv]
+
+Lightning attention, per head with state S [dk, dv]:
+
+    q, k, v   = silu(W_q x), silu(W_k x), silu(W_v x)
+    S <- decay[h] S + k v^T;  o = S^T q
+    out       = W_o [ heads' o / rms(all heads together) * norm * sigmoid(W_g x) ]
+
 The state, the decays, gates, unit norms, angles and read-outs are float32 in both dtypes; the
 projections and what follows the gate are in the activation dtype.
 """
@@ -69,7 +83,8 @@ class ProjectedMixer(Mixer):
         raise NotImplementedError
 
     def run(self, proj: torch.Tensor, ctx: StepContext, cache: "CacheBinding | None",
-            ahead: "NormAhead | None" = None) -> "torch.Tensor | None":
+            ahead: "NormAhead | None" = None,
+            out_dtype: "torch.dtype | None" = None) -> "torch.Tensor | None":
         raise NotImplementedError
 
     def finish_load(self) -> None:
@@ -102,14 +117,18 @@ class ProjectedMixer(Mixer):
         return self.run(proj, ctx, cache, ahead=ahead)
 
     def project_out(self, rows: torch.Tensor, name: str, ctx: StepContext,
-                    ahead: "NormAhead | None") -> "torch.Tensor | None":
+                    ahead: "NormAhead | None",
+                    out_dtype: "torch.dtype | None" = None) -> "torch.Tensor | None":
         """The output product; with ``ahead`` it joins the residual and does the next norm's
-        work (and nothing is returned)."""
+        work (and nothing is returned).  ``out_dtype``: float32 for a result that is combined
+        with another before it is rounded."""
         if ahead is not None:
             ops.linear(rows, self.w_o, out=ahead.rows, status=ctx.status, after=ahead)
             return None
-        out = ctx.buffer(name, (rows.shape[0], self.width))
-        ops.linear(rows, self.w_o, out=out, status=ctx.status)
+        if out_dtype is not None and out_dtype != self.dtype:
+            name += ".wide"                       # a buffer of its own: no two dtypes under a name
+        out = ctx.buffer(name, (rows.shape[0], self.width), out_dtype)
+        ops.linear(rows, self.w_o, out=out, out_dtype=out.dtype, status=ctx.status)
         return out
 
 
@@ -173,7 +192,7 @@ class GatedDeltaRule(ProjectedMixer):
         # the state matrices, then the convolution's last taps - 1 inputs
         return StateSpec((self.state_rows + (self.taps - 1) * self.channels,), torch.float32)
 
-    def run(self, proj, ctx, cache, ahead=None):
+    def run(self, proj, ctx, cache, ahead=None, out_dtype=None):
         if cache is None or cache.kind != "state":
             raise ValueError("the gated delta rule needs a state slot")
         if not cache.writes:
@@ -199,7 +218,7 @@ class GatedDeltaRule(ProjectedMixer):
                       keep=(proj, self.state_rows, self.channels, self.taps))
         gated = ctx.buffer("delta.gated", (n, H * dv))
         rk.head_gate(o, gate, self.norm, gated, H, dv, self.eps)
-        return self.project_out(gated, "delta.out", ctx, ahead)
+        return self.project_out(gated, "delta.out", ctx, ahead, out_dtype=out_dtype)
 
 
 class Retention(ProjectedMixer):
@@ -239,7 +258,7 @@ class Retention(ProjectedMixer):
     def cache_spec(self):
         return StateSpec((self.heads * self.dk * self.dv,), torch.float32)
 
-    def run(self, proj, ctx, cache, ahead=None):
+    def run(self, proj, ctx, cache, ahead=None, out_dtype=None):
         if cache is None or cache.kind != "state":
             raise ValueError("retention needs a state slot")
         if not cache.writes:
@@ -253,8 +272,128 @@ class Retention(ProjectedMixer):
                       dv, ctx, decay=self.decay)
         gated = ctx.buffer("retention.gated", (n, H * dv))
         rk.head_gate(o, proj[:, self.g_col: self.g_col + H * dv], None, gated, H, dv, self.eps)
-        return self.project_out(gated, "retention.out", ctx, ahead)
+        return self.project_out(gated, "retention.out", ctx, ahead, out_dtype=out_dtype)
 
 
+class GeneralizedDeltaRule(ProjectedMixer):
+    kind = "generalized_delta_rule"
+
+    def __init__(self, width: int, heads: int, key_dim: int, eps: float, dtype: torch.dtype,
+                 device: torch.device, rank: "int | None" = None) -> None:
+        """Keys, values and read-out vectors all have ``key_dim`` features a head.  ``rank``: of
+        the decay's low-rank projection; None: whatever the weight file holds."""
+        super().__init__(dtype, device)
+        if key_dim > rk.max_key_dim():
+            raise ValueError(f"generalized_delta_rule: key size {key_dim} is beyond "
+                             f"{rk.max_key_dim()}")
+        self.width, self.heads, self.dk, self.eps, self.rank = width, heads, key_dim, eps, rank
+        self.rows = heads * key_dim
+
+    def tensors(self):
+        d, n, r = self.width, self.rows, -1 if self.rank is None else self.rank
+        return {"r": ((n, d), "matrix"), "k": ((n, d), "matrix"), "v": ((n, d), "matrix"),
+                "g": ((n, d), "matrix"), "a": ((n, d), "matrix"), "a.b": ((n,), "bias"),
+                "w1": ((r, d), "matrix"), "w2": ((n, r), "matrix"), "w0": ((n,), "bias"),
+                "norm": ((n,), "vector"), "o": ((d, n), "matrix")}
+
+    def load(self, tensors):
+        if tensors["w1"].shape[0] != tensors["w2"].shape[1]:
+            raise ValueError("generalized_delta_rule: the two halves of the decay's low-rank "
+                             "projection do not have the same rank")
+        self._host_in, offsets = stack_segments([
+            torch.cat((tensors["r"], tensors["k"], tensors["v"], tensors["g"], tensors["a"]),
+                      dim=0), tensors["w1"]])
+        self.w1_col, self.w_rank = offsets[1], tensors["w1"].shape[0]
+        self.w_w2 = compute_matrix(tensors["w2"], self.dtype, self.device)
+        self.w_o = compute_matrix(tensors["o"], self.dtype, self.device)
+        self.w0 = vector32(tensors["w0"], self.device)
+        self.a_bias = vector32(tensors["a.b"], self.device)
+        self.norm = vector32(tensors["norm"], self.device)
+        self.w_in = None
+
+    def input_matrix(self) -> torch.Tensor:
+        return self._host_in
+
+    def cache_spec(self):
+        return StateSpec((self.heads * self.dk * self.dk,), torch.float32)
+
+    def run(self, proj, ctx, cache, ahead=None, out_dtype=None):
+        if cache is None or cache.kind != "state":
+            raise ValueError("the generalized delta rule needs a state slot")
+        if not cache.writes:
+            raise ValueError("the generalized delta rule cannot read another run's state: it "
+                             "advances it")
+        n, f32, H, dk, rows = proj.shape[0], torch.float32, self.heads, self.dk, self.rows
+        inner = proj[:, self.w1_col: self.w1_col + self.w_rank]
+        ops.activation(inner, inner, "tanh")
+        wl = ctx.buffer("gdelta.wl", (n, rows), f32)
+        ops.linear(inner, self.w_w2, out=wl, out_dtype=f32, status=ctx.status)
+        rr = ctx.buffer("gdelta.r", (n, rows), f32)
+        kk = ctx.buffer("gdelta.k", (n, rows), f32)
+        ww = ctx.buffer("gdelta.w", (n, rows), f32)
+        zz = ctx.buffer("gdelta.z", (n, rows), f32)
+        rk.gdelta_prep(proj, 0, rows, 4 * rows, wl, self.w0, self.a_bias, rr, kk, ww, zz, H, dk)
+        o = ctx.buffer("gdelta.o", (n, rows), f32)
+        rk.state_scan(rr, kk, proj[:, 2 * rows: 3 * rows], cache.state, o, H, H, dk, dk, ctx,
+                      g=ww, z=zz)
+        gated = ctx.buffer("gdelta.gated", (n, rows))
+        rk.head_gate(o, proj[:, 3 * rows: 4 * rows], self.norm, gated, H, dk, self.eps,
+                     spanning=True)
+        return self.project_out(gated, "gdelta.out", ctx, ahead, out_dtype=out_dtype)
+
+
+class LightningAttention(ProjectedMixer):
+    kind = "lightning_attention"
+
+    def __init__(self, width: int, heads: int, key_dim: int, value_dim: int, decay, eps: float,
+                 dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__(dtype, device)
+        if len(decay) != heads:
+            raise ValueError(f"lightning_attention: {len(decay)} decays for {heads} heads")
+        if key_dim > rk.max_key_dim():
+            raise ValueError(f"lightning_attention: key size {key_dim} is beyond "
+                             f"{rk.max_key_dim()}")
+        self.width, self.heads, self.dk, self.dv, self.eps = width, heads, key_dim, value_dim, eps
+        self.decay = torch.tensor([float(x) for x in decay], dtype=torch.float32, device=device)
+
+    def tensors(self):
+        d, hk, hv = self.width, self.heads * self.dk, self.heads * self.dv
+        return {"q": ((hk, d), "matrix"), "k": ((hk, d), "matrix"), "v": ((hv, d), "matrix"),
+                "g": ((hv, d), "matrix"), "norm": ((hv,), "vector"), "o": ((d, hv), "matrix")}
+
+    def load(self, tensors):
+        self._host_in, offsets = stack_segments([
+            torch.cat((tensors["q"], tensors["k"], tensors["v"]), dim=0), tensors["g"]])
+        self.g_col = offsets[1]
+        self.w_o = compute_matrix(tensors["o"], self.dtype, self.device)
+        self.norm = vector32(tensors["norm"], self.device)
+        self.w_in = None
+
+    def input_matrix(self) -> torch.Tensor:
+        return self._host_in
+
+    def cache_spec(self):
+        return StateSpec((self.heads * self.dk * self.dv,), torch.float32)
+
+    def run(self, proj, ctx, cache, ahead=None, out_dtype=None):
+        if cache is None or cache.kind != "state":
+            raise ValueError("lightning attention needs a state slot")
+        if not cache.writes:
+            raise ValueError("lightning attention cannot read another run's state: it advances it")
+        n, f32, H, dk, dv = proj.shape[0], torch.float32, self.heads, self.dk, self.dv
+        qkv = ctx.buffer("lightning.qkv", (n, H * (2 * dk + dv)), f32)
+        rk.silu_rows(proj[:, : H * (2 * dk + dv)], qkv)
+        o = ctx.buffer("lightning.o", (n, H * dv), f32)
+        rk.state_scan(qkv[:, : H * dk], qkv[:, H * dk: 2 * H * dk], qkv[:, 2 * H * dk:],
+                      cache.state, o, H, H, dk, dv, ctx, decay=self.decay)
+        gated = ctx.buffer("lightning.gated", (n, H * dv))
+        # one root mean square for all heads together: a single "head" as wide as the row
+        rk.head_gate(o, proj[:, self.g_col: self.g_col + H * dv], self.norm, gated, 1, H * dv,
+                     self.eps, spanning=True)
+        return self.project_out(gated, "lightning.out", ctx, ahead, out_dtype=out_dtype)
+
+
+register_mixer("generalized_delta_rule", GeneralizedDeltaRule)
+register_mixer("lightning_attention", LightningAttention)
 register_mixer("gated_delta_rule", GatedDeltaRule)
 register_mixer("retention", Retention)
