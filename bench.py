@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload headline|mixed|long|fp32|vomotar] [--layers L]
+                    [--workload headline|mixed|long|fp32|vomotar|sebilorn] [--layers L]
 
 The default (``headline``) has the TinyLlama-1.1B layer sizes in bfloat16.  A step is one decode
 step of a batch of 8 requests whose prompts of 512 tokens are in the cache; K steps are timed with
@@ -34,6 +34,12 @@ Other workloads, each with its own line (the number of layers is named beside th
   beside retention) at the headline's width, feed-forward and vocabulary, beside the Llama decoder
   with the same number of layers: decode at batch 8 and 64 and a prompt of 2,048 tokens for both,
   and every kernel that is the design's own, alone, against its roofline.
+* ``sebilorn``: the Sebilorn architecture (windowed attention with kept first tokens, a layer that
+  reads the layer before it's keys and values, gated attention beside the generalized delta rule,
+  lightning attention; layer norms, squared-relu feed-forward) at the same width, feed-forward and
+  vocabulary, beside Vomotar and Llama with the same number of layers: decode at batch 8 and 64
+  and a prompt of 2,048 tokens, and every kernel of the design alone against its roofline, each
+  beside the like kernel of the other models.
 """
 
 from __future__ import annotations
@@ -559,6 +565,252 @@ def workload_vomotar(args, warmup: int, steps: int) -> int:
     return 0
 
 
+def sebilorn_shape(layers: int) -> dict:
+    """A Sebilorn model of the headline's width, feed-forward and vocabulary: windowed attention, a
+    layer that reads its keys and values, attention beside the generalized delta rule, lightning
+    attention, in turn."""
+    mlp = {"kind": "dense", "ff": MODEL["intermediate_size"]}
+    rot = {"dims": 128, "base": 500000.0,
+           "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+
+    def attention(kv_from=None):
+        mixer = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "softcap": 30.0, "mask": {"size": 1024, "keep_first": 4}, "rot": rot}
+        if kv_from is not None:
+            mixer["kv_from"] = kv_from
+        return {"type": "attention", "mixer": mixer, "mlp": mlp}
+
+    parallel = {"type": "parallel",
+                "mixer": {"left": {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128,
+                                   "scale": 128 ** -0.5, "rot": {"dims": 64, "base": 10000.0}},
+                          "right": {"heads": 16, "dim": 128, "rank": 64},
+                          "left_scale": 0.5, "right_scale": 0.5},
+                "mlp": mlp}
+    lightning = {"type": "lightning",
+                 "mixer": {"heads": 16, "dim": 128, "vdim": 128,
+                           "decay": [1.0 - 2.0 ** -(4 + i % 8) for i in range(16)]},
+                 "mlp": mlp}
+    out = []
+    for i in range(layers):
+        out.append([attention(), attention(i - 1), parallel, lightning][i % 4])
+    return {"architecture": "Sebilorn", "vocab": MODEL["vocab_size"],
+            "width": MODEL["hidden_size"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "logit_softcap": 30.0, "layers": out}
+
+
+def sebilorn_folder(layers: int) -> str:
+    from distengine_b200.weights import write_random_model
+    folder = os.path.join(tempfile.gettempdir(), f"distengine_b200-bench-{os.getuid()}",
+                          f"sebilorn-shape-{layers}-layers-seed0-bf16")
+    marker = os.path.join(folder, ".complete")
+    if not os.path.isfile(marker):
+        print("[bench] writing the random-weights model folder ...", file=sys.stderr, flush=True)
+        write_random_model(sebilorn_shape(layers), folder, seed=0, dtype="bfloat16",
+                           norm_init="uniform")
+        with open(marker, "w") as handle:
+            handle.write("ok")
+    return folder
+
+
+def sebilorn_kernels(peak: dict) -> list[dict]:
+    """The design's kernels alone at the sizes of ``sebilorn_shape``, for a prompt of 2,048 tokens
+    and for a decode step of 64 sequences, as ``vomotar_kernels`` measures its own; the norm and
+    the activation are measured beside the RMS norm and silu * up of the other models."""
+    from types import SimpleNamespace
+    import numpy as np
+    import torch
+    from distengine_b200.kernels import ops
+    from distengine_b200.kernels import recurrent as rk
+    from distengine_b200.kernels.attention_plan import build_plan
+    from distengine_b200.parts.window_attention import rotary_frequencies
+    dev, bf16, f32 = "cuda:0", torch.bfloat16, torch.float32
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fp32_peak = 148 * 128 * 2 * 1.965e9          # fused multiply-adds of the CUDA cores
+
+    def ctx_of(lens, pos0):
+        lens = np.asarray(lens, dtype=np.int32)
+        pos0 = np.asarray(pos0, dtype=np.int32)
+        qstart = (np.cumsum(lens) - lens).astype(np.int32)
+        seq = np.repeat(np.arange(len(lens), dtype=np.int32), lens)
+        slots = np.arange(len(lens), dtype=np.int32)
+        pos = pos0[seq] + np.arange(lens.sum(), dtype=np.int32) - qstart[seq]
+        d = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+        return SimpleNamespace(n_seqs=len(lens), token_seq=d(seq), token_slot=d(slots[seq]),
+                               positions=d(pos), seq_slot=d(slots), seq_qstart=d(qstart),
+                               seq_qlen=d(lens), seq_pos0=d(pos0),
+                               host=SimpleNamespace(seq_qlen=lens, seq_pos0=pos0),
+                               status=torch.zeros(1, dtype=torch.int32, device=dev))
+
+    def timed(fn, repeats=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(repeats):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(times)
+
+    out = []
+
+    def record(name, case, us, bytes_=0, flops=0, like=""):
+        entry = {"kernel": name, "case": case, "us": round(us, 1), "like": like}
+        hbm_us = bytes_ / (peak["hbm_gbs"] * 1e3)
+        fma_us = flops / fp32_peak * 1e6
+        entry["roofline_us"] = round(max(hbm_us, fma_us), 1)
+        entry["bound"] = "hbm" if hbm_us >= fma_us else "fp32 fma"
+        entry["frac"] = round(max(hbm_us, fma_us) / us, 3)
+        out.append(entry)
+
+    H, G, dk, dv, width, ff = 16, 4, 128, 128, MODEL["hidden_size"], MODEL["intermediate_size"]
+    window, keep, page = 1024, 4, 16
+    for case, lens, pos0 in (("prompt of 2,048", [2048], [0]), ("decode, 64 sequences", [1] * 64,
+                                                                 [600] * 64)):
+        ctx = ctx_of(lens, pos0)
+        n, s = int(sum(lens)), len(lens)
+        # norms: the layer norm beside the RMS norm
+        resid = torch.randn(n, width, device=dev)
+        delta = torch.randn(n, width, device=dev).to(bf16)
+        wv, bv = torch.rand(width, device=dev).to(bf16), torch.rand(width, device=dev).to(bf16)
+        normed = torch.empty(n, width, dtype=bf16, device=dev)
+        us = timed(lambda: ops.add_layernorm(resid, delta, wv, bv, 1e-5, normed))
+        record("add_layernorm", case, us, bytes_=n * width * (4 + 4 + 2 + 2), like="add_rmsnorm")
+        us = timed(lambda: ops.add_rmsnorm(resid, delta, wv, 1e-5, normed))
+        record("add_rmsnorm (other models)", case, us, bytes_=n * width * (4 + 4 + 2 + 2))
+        # activations: the squared relu beside silu * up
+        up = torch.randn(n, 2 * ff, device=dev).to(bf16)
+        act = torch.empty(n, ff, dtype=bf16, device=dev)
+        us = timed(lambda: ops.activation(up[:, :ff], act, "relu2"))
+        record("activation (squared relu)", case, us, bytes_=n * ff * 4, like="silu_mul")
+        us = timed(lambda: ops.silu_mul(up, act))
+        record("silu_mul (other models)", case, us, bytes_=n * ff * 6)
+        # windowed attention: 16 heads on 4 kv heads, window 1,024, 4 kept tokens
+        longest = max(p + l for p, l in zip(pos0, lens))
+        pages_seq = (longest + page - 1) // page
+        kp = torch.randn(s * pages_seq, G, page, dk, device=dev).to(bf16)
+        vp = torch.randn(s * pages_seq, G, page, dv, device=dev).to(bf16)
+        table = torch.arange(s * pages_seq, dtype=torch.int32, device=dev).view(s, pages_seq)
+        aproj = torch.randn(n, H * dk + G * (dk + dv) + H * dv, device=dev).to(bf16)
+        fk = rotary_frequencies(500000.0, dk, (8.0, 1.0, 4.0, 8192)).to(dev)
+        fv = rotary_frequencies(500000.0, dv).to(dev)
+        us = timed(lambda: rk.kv_write_rotated(aproj, fk, dk, fv, H, G, dk, dv, kp, vp, table,
+                                               True, ctx))
+        record("kv_write_rotated", case, us, bytes_=n * (2 * H * dk + 2 * G * (dk + dv)) * 2,
+               like="kv_write_normed")
+        rows = rk.chunk_rows_per_tile(bf16, dk, dv, n > s)
+        plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H // G, G, rows, 0, chunk=0)
+        items = torch.from_numpy(plan.items).to(dev)
+        raw = torch.empty(n, H * dv, device=dev)
+        sight = dict(window=window, keep_first=keep, softcap=30.0)
+        if n == s and rk.chunk_decode_ok(bf16, H, G, dk, dv):      # as the mixer chooses
+            us = timed(lambda: rk.chunk_attention_decode(aproj, raw, kp, vp, table, None, None, H,
+                                                         G, dk, dv, 0.09, 0, ctx, **sight))
+        else:
+            us = timed(lambda: rk.chunk_attention(aproj, raw, kp, vp, table, items, None, None, H,
+                                                  G, dk, dv, 0.09, 0, ctx, tile_rows=rows,
+                                                  **sight))
+        keys = sum(sum(min(p + i + 1, window + keep) for i in range(l))
+                   for p, l in zip(pos0, lens))
+        record("window_attention", case, us,
+               bytes_=sum(min(p + l, window + keep + l) for p, l in zip(pos0, lens))
+               * G * (dk + dv) * 2, flops=2 * keys * H * (dk + dv), like="chunk_attention")
+        ao = torch.empty(n, H * dv, dtype=bf16, device=dev)
+        gate = aproj[:, H * dk + G * (dk + dv):]
+        us = timed(lambda: rk.attention_finish(raw, fv, gate, ao, H, dv, ctx))
+        record("attention_finish", case, us, bytes_=n * H * dv * (4 + 2 + 2), like="head_gate")
+        # the generalized delta rule: 16 heads of 128 x 128
+        rows_ = H * dk
+        dproj = torch.randn(n, 5 * rows_ + 64, device=dev).to(bf16)
+        wl = torch.randn(n, rows_, device=dev)
+        vec = torch.randn(rows_, device=dev)
+        rr, kk, ww, zz = (torch.empty(n, rows_, device=dev) for _ in range(4))
+        dots = torch.empty(n, 2 * H, device=dev)
+        us = timed(lambda: rk.gdelta_prep(dproj, 0, rows_, 4 * rows_, wl, vec, vec, rr, kk, ww, zz,
+                                          dots, H, dk))
+        record("gdelta_prep", case, us, bytes_=n * rows_ * (3 * 2 + 4 + 4 * 4), like="delta_prep")
+        state = torch.zeros(s, H * dk * dk, device=dev)
+        o = torch.empty(n, rows_, device=dev)
+        us = timed(lambda: rk.state_scan(rr, kk, dproj[:, 2 * rows_: 3 * rows_], state, o, H, H,
+                                         dk, dk, ctx, g=ww, z=zz, dots=dots))
+        record("state_scan (generalized delta rule)", case, us,
+               bytes_=2 * s * H * dk * dk * 4 + n * rows_ * (4 * 4 + 2 + 4),
+               flops=n * H * dk * dk * 9, like="state_scan (delta rule)")
+        gated = torch.empty(n, rows_, dtype=bf16, device=dev)
+        us = timed(lambda: rk.head_gate(o, dproj[:, 3 * rows_: 4 * rows_], vec, gated, H, dk, 1e-5,
+                                        spanning=True))
+        record("head_gate (weight over the heads)", case, us, bytes_=n * rows_ * (4 + 2 + 2),
+               like="head_gate")
+        us = timed(lambda: rk.head_gate(o, dproj[:, 3 * rows_: 4 * rows_], vec, gated, 1, rows_,
+                                        1e-5, spanning=True))
+        record("head_gate (one norm a row)", case, us, bytes_=n * rows_ * (4 + 2 + 2),
+               like="head_gate")
+        # lightning attention: silu of q, k, v, then the scan with a decay per head
+        qkv = torch.empty(n, 3 * rows_, device=dev)
+        us = timed(lambda: rk.silu_rows(dproj[:, : 3 * rows_], qkv))
+        record("silu_rows", case, us, bytes_=n * 3 * rows_ * (2 + 4), like="retention_prep")
+        decay = torch.full((H,), 0.99, device=dev)
+        us = timed(lambda: rk.state_scan(qkv[:, :rows_], qkv[:, rows_: 2 * rows_],
+                                         qkv[:, 2 * rows_:], state, o, H, H, dk, dk, ctx,
+                                         decay=decay))
+        record("state_scan (lightning)", case, us,
+               bytes_=2 * s * H * dk * dk * 4 + n * rows_ * 4 * 4, flops=n * H * dk * dk * 5,
+               like="state_scan (retention)")
+        a32, b32 = torch.randn(n, width, device=dev), torch.randn(n, width, device=dev)
+        mo = torch.empty(n, width, dtype=bf16, device=dev)
+        us = timed(lambda: ops.scaled_sum(a32, b32, 0.5, 0.5, mo))
+        record("scaled_sum", case, us, bytes_=n * width * 10, like="mean_of_normed")
+    return out
+
+
+def workload_sebilorn(args, warmup: int, steps: int) -> int:
+    """Sebilorn beside Vomotar and Llama at equal width, feed-forward, vocabulary and number of
+    layers."""
+    import numpy as np
+    import torch
+    from distengine_b200 import Engine, EngineConfig
+    peak, peak_kind = peaks()
+    layers = args.layers
+    rng = np.random.default_rng(0)
+    vocab = MODEL["vocab_size"]
+    result = {}
+    for name, folder in (("sebilorn", sebilorn_folder(layers)),
+                         ("vomotar", vomotar_folder(layers)), ("llama", model_folder(layers))):
+        pages = (64 * (PROMPT + 8 + warmup + steps) + PREFILL) // PAGE + 64
+        engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=pages,
+                                             decode_batch_size=64, max_batch_tokens=PREFILL,
+                                             max_model_len=4096, use_graphs=not args.no_graphs))
+        prefill_ms, prefill_step_ms = timed_prefill(engine, PREFILL, rng, vocab, repeats=5)
+        entry = {"prefill_2048": {"ms": round(prefill_ms, 3),
+                                  "ms_with_host_prepare": round(prefill_step_ms, 3),
+                                  "tokens_per_s": round(PREFILL / prefill_ms * 1e3, 1)}}
+        for batch in (8, 64):
+            ms, launches, _, clocks = timed_decode(engine, batch, PROMPT, steps, warmup, rng, vocab)
+            entry[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4),
+                                         "tokens_per_s": round(batch / ms * 1e3, 1),
+                                         "gpu_launches": int(launches), "clocks": clocks}
+        result[name] = entry
+        del engine
+        torch.cuda.empty_cache()
+    mine = result["sebilorn"]["decode_b8"]
+    print(json.dumps({
+        "metric": "decode tokens/s at batch 8, Sebilorn at the TinyLlama-1.1B width",
+        "value": mine["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": mine["ms_per_step"], "dtype": "bf16",
+        "higher_is_better": True, "data": "synthetic", "impl": "ours", "workload": "sebilorn",
+        "config": {"layers": layers, "width": MODEL["hidden_size"],
+                   "ff": MODEL["intermediate_size"], "vocab": vocab, "seq_len": PROMPT,
+                   "page_size": PAGE, "peaks": peak_kind, "shape": sebilorn_shape(4)["layers"],
+                   "l2": "weights larger than L2 are read every step; kernels alone: L2 flushed"},
+        "gpu_launches": mine["gpu_launches"], "clocks": mine["clocks"],
+        "models": result, "kernels": sebilorn_kernels(peak),
+        "kernels_vomotar": vomotar_kernels(peak)}))
+    return 0
+
+
 def workload_long(args, warmup: int, steps: int) -> int:
     """Llama-3-8B layer sizes: 64 requests with prompts of 4,096 tokens (fed as portions of 4,096
     tokens), then decode steps at batch 64 over the long cache; vocabulary 128,256."""
@@ -760,9 +1012,10 @@ def main() -> int:
                         help="print one decode step's in-kernel timeline (kernels built with "
                              "DISTENGINE_B200_DEFINES=DE_TRACE)")
     parser.add_argument("--workload", default="headline",
-                        choices=["headline", "mixed", "long", "fp32", "vomotar"])
+                        choices=["headline", "mixed", "long", "fp32", "vomotar", "sebilorn"])
     args = parser.parse_args()
-    if args.workload in ("mixed", "long", "vomotar") and "--layers" not in " ".join(sys.argv):
+    if (args.workload in ("mixed", "long", "vomotar", "sebilorn")
+            and "--layers" not in " ".join(sys.argv)):
         args.layers = 8          # of the 32 that the Llama-2-7B and Llama-3-8B shapes have
 
     if args.gpus != 1:
@@ -775,7 +1028,8 @@ def main() -> int:
         return timeline(args)
     if args.workload != "headline":
         return {"mixed": workload_mixed, "long": workload_long, "fp32": workload_fp32,
-                "vomotar": workload_vomotar}[args.workload](args, warmup, steps)
+                "vomotar": workload_vomotar,
+                "sebilorn": workload_sebilorn}[args.workload](args, warmup, steps)
 
     import numpy as np
     import torch

@@ -53,6 +53,18 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* 33 floats 
     return scratch[32];
 }
 
+// Activations by number (the C interface's `kind`): 0 the square of relu, 1 tanh, 2 silu,
+// 3 gelu in its tanh form.
+__device__ __forceinline__ float de_activate(float x, int kind) {
+    if (kind == 0) {
+        const float r = fmaxf(x, 0.0f);
+        return r * r;
+    }
+    if (kind == 1) return tanhf(x);
+    if (kind == 2) return x / (1.0f + expf(-x));
+    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+}
+
 static inline int de_check(cudaError_t e) { return e == cudaSuccess ? 0 : (int)e; }
 
 // ---------------------------------------------------------------------------------------------

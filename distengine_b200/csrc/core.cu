@@ -779,16 +779,6 @@ DE_EXPORT int de_add_layernorm(int dtype, int weight_dtype, float* resid, const 
 //   kind 0: relu(x)^2     kind 1: tanh(x)     kind 2: silu(x)     kind 3: gelu (tanh form)
 // x [n, cols] with row stride ldx, out [n, cols] with row stride ldo (out may be x).
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ float activate(float x, int kind) {
-    if (kind == 0) {
-        const float r = fmaxf(x, 0.0f);
-        return r * r;
-    }
-    if (kind == 1) return tanhf(x);
-    if (kind == 2) return x / (1.0f + expf(-x));
-    return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
-}
-
 template <typename T>
 __global__ void activation_kernel(const T* __restrict__ x, int ldx, T* __restrict__ out, int ldo,
                                   int cols, size_t total, int kind) {
@@ -798,7 +788,7 @@ __global__ void activation_kernel(const T* __restrict__ x, int ldx, T* __restric
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t n = idx / cols;
         const int i = (int)(idx - n * cols);
-        out[n * ldo + i] = from_float<T>(activate(to_float(x[n * ldx + i]), kind));
+        out[n * ldo + i] = from_float<T>(de_activate(to_float(x[n * ldx + i]), kind));
     }
 }
 
@@ -815,7 +805,7 @@ __global__ void activation_vec_kernel(const T* __restrict__ x, int ldx, T* __res
         float v[4];
         Vec4<T>::load(x + n * ldx + i, v);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[e] = activate(v[e], kind);
+        for (int e = 0; e < 4; ++e) v[e] = de_activate(v[e], kind);
         Vec4<T>::store(out + n * ldo + i, v);
     }
 }

@@ -81,6 +81,8 @@ struct Norm {
     int ld_resid;
     const __nv_bfloat16* weight;
     float* out_parts;
+    // an activation on the (ungated) product's outputs: 0 none, else de_activate's kind + 1
+    int act;
 };
 
 // blocks of k that a warp loads before it multiplies any of them: 8 to 16 loads of 16 bytes in
@@ -306,6 +308,11 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const __nv_bfl
             const float up = __bfloat162float(__float2bfloat16_rn(v[SETS - 1]));
             y = gate / (1.0f + expf(-gate)) * up;
         }
+        if constexpr (!GATED) {
+            // rounded to the output type before the activation, as a separate product and
+            // activation would do
+            if (norm.act != 0) y = de_activate(to_float(to_out<OutT>(y)), norm.act - 1);
+        }
         if constexpr (NORM && !GATED) {
             if (norm.resid != nullptr) {
                 // the branch is rounded to bfloat16 before it joins the residual, as when it goes
@@ -382,13 +389,16 @@ int check(int m_rows, int k_dim, int ldx, int ldw, const void* x, const void* w)
 DE_EXPORT int de_linear_small_max_rows() { return 32; }
 
 // out_f32: 1 for float32 output, 0 for bfloat16.  gated: w is [2 * n_out, k], gate rows first.
+// act: 0, or 1 + the kind of activation (de_activate) that the outputs of an ungated product pass.
 DE_EXPORT int de_linear_small(const void* x, int ldx, const void* w, int ldw, void* out, int ldo,
-                              int m_rows, int n_out, int k_dim, int out_f32, int gated,
+                              int m_rows, int n_out, int k_dim, int out_f32, int gated, int act,
                               void* stream) {
     if (m_rows <= 0 || n_out <= 0) return 0;
     if (int code = check(m_rows, k_dim, ldx, ldw, x, w)) return code;
+    if (act < 0 || act > 4 || (act && gated)) return -4;
     cudaStream_t s = (cudaStream_t)stream;
-    const Norm none = {};
+    Norm none = {};
+    none.act = act;
     if (gated) {
         if (out_f32) return -4;
         return pick<true, false, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim,

@@ -160,13 +160,16 @@ __global__ void retention_prep_kernel(const T* __restrict__ proj, int ld,
 //   wl float32 [N, H dk]: the low-rank decay projection's output
 //   rr = r, kk = k as float32;  w = exp(-exp(-1/2) * sigmoid(wl + w0))
 //   z  = sigmoid(a + a_bias) * k / (sum over the head of k^2 + 1e-6)
+//   dots [N, H, 2] = (z . r, k . r) per head: what the scan's read-out needs of them, the same for
+//   every column of the state
 // ------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void gdelta_prep_kernel(const T* __restrict__ proj, int ld, int r_col, int k_col,
                                    int a_col, const float* __restrict__ wl,
                                    const float* __restrict__ w0, const float* __restrict__ a_bias,
                                    float* __restrict__ rr, float* __restrict__ kk,
-                                   float* __restrict__ ww, float* __restrict__ zz, int H, int dk) {
+                                   float* __restrict__ ww, float* __restrict__ zz,
+                                   float* __restrict__ dots, int H, int dk) {
     const int n = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const T* row = proj + (size_t)n * ld;
@@ -181,13 +184,23 @@ __global__ void gdelta_prep_kernel(const T* __restrict__ proj, int ld, int r_col
             ss = fmaf(x, x, ss);
         }
         const float inv2 = 1.0f / (warp_sum(ss) + 1e-6f);
+        float zr = 0.0f, kr = 0.0f;
         for (int i = lane; i < dk; i += 32) {
             const int c = h * dk + i;
-            const float x = to_float(ks[i]);
+            const float x = to_float(ks[i]), r = to_float(row[r_col + c]);
+            const float z = sigmoid_f(to_float(row[a_col + c]) + a_bias[c]) * x * inv2;
             kk[base + c] = x;
-            rr[base + c] = to_float(row[r_col + c]);
-            zz[base + c] = sigmoid_f(to_float(row[a_col + c]) + a_bias[c]) * x * inv2;
+            rr[base + c] = r;
+            zz[base + c] = z;
             ww[base + c] = expf(-rate * sigmoid_f(wl[base + c] + w0[c]));
+            zr = fmaf(z, r, zr);
+            kr = fmaf(x, r, kr);
+        }
+        zr = warp_sum(zr);
+        kr = warp_sum(kr);
+        if (lane == 0) {
+            dots[((size_t)n * H + h) * 2] = zr;
+            dots[((size_t)n * H + h) * 2 + 1] = kr;
         }
     }
     pdl_trigger();
@@ -246,7 +259,7 @@ __device__ __forceinline__ int state_row(int r, int l) {      // register r of s
 
 // MODE 0: retention; 1: the delta rule (g, beta); 2: the generalized delta rule (g = w, z).
 template <typename VT, int R, int MODE, int COLS, int LANES>
-__global__ void __launch_bounds__(COLS * LANES)
+__global__ void __launch_bounds__(COLS * LANES, (MODE == 2 && R <= 32) ? 384 / (COLS * LANES) : 1)
 scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
             const VT* __restrict__ v, int ldv, const float* __restrict__ g, int ldg,
             const float* __restrict__ beta, int ldb, const float* __restrict__ z, int ldz,
@@ -325,7 +338,7 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
         cp_async_commit();
     };
     // a batch's values and gates do not depend on the state: they are asked for a batch ahead
-    float nv[TB], nb[TB];
+    float nv[TB], nb[TB], nc[TB];
     auto fetch = [&](int b) {
         const int count = min(TB, qlen - b * TB);
 #pragma unroll
@@ -333,6 +346,10 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
             const size_t tok = (size_t)(tok0 + b * TB + t);
             nv[t] = (live && t < count) ? to_float(v[tok * ldv + h * dv + col]) : 0.0f;
             nb[t] = (DELTA && t < count) ? beta[tok * ldb + h] : 0.0f;
+            if (MODE == 2) {                         // (z . r, k . r) of the token's head
+                nb[t] = t < count ? beta[tok * ldb + 2 * h] : 0.0f;
+                nc[t] = t < count ? beta[tok * ldb + 2 * h + 1] : 0.0f;
+            }
         }
     };
 
@@ -343,11 +360,12 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
     }
     for (int b = 0; b < batches; ++b) {
         const int count = min(TB, qlen - b * TB);
-        float vt[TB], bt[TB];
+        float vt[TB], bt[TB], ct[TB];
 #pragma unroll
         for (int t = 0; t < TB; ++t) {
             vt[t] = nv[t];
             bt[t] = nb[t];
+            ct[t] = MODE == 2 ? nc[t] : 0.0f;
         }
         if (b + 1 < batches) {
             issue(b + 1);
@@ -370,43 +388,38 @@ scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, i
             // last thing a token does, off the next token's critical path but for S itself.
             if (MODE == 2) {
                 // With p = k^T S (old state) the new state is diag(w) S - z p + k v and the
-                // read-out (w S)^T r - p (z . r) + v (k . r): four sums in one pass over the
-                // quarter's rows, one butterfly for all four, the update of S last.
+                // read-out (w S)^T r - p (z . r) + v (k . r); z . r and k . r do not depend on the
+                // column and come with the token.  Two sums in one pass over the quarter's rows,
+                // one butterfly for both, the update of S last.
                 const float4* w4 =
                     reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD + 2 * PD);
                 const float4* z4 =
                     reinterpret_cast<const float4*>(src + (size_t)t * VECS * PD + 3 * PD);
-                float pa = 0.0f, pb = 0.0f, oa = 0.0f, ob = 0.0f, za = 0.0f, zb = 0.0f, ka = 0.0f,
-                      kb = 0.0f;
+                float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
+                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
                 for (int r = 0; r < R / 4; ++r) {
-                    const float4 ww = w4[r], kk = k4[r], qq = q4[r], zz = z4[r];
-                    pa = fmaf(S[4 * r + 0], kk.x, pa); S[4 * r + 0] *= ww.x; oa = fmaf(S[4 * r + 0], qq.x, oa);
-                    pb = fmaf(S[4 * r + 1], kk.y, pb); S[4 * r + 1] *= ww.y; ob = fmaf(S[4 * r + 1], qq.y, ob);
-                    pa = fmaf(S[4 * r + 2], kk.z, pa); S[4 * r + 2] *= ww.z; oa = fmaf(S[4 * r + 2], qq.z, oa);
-                    pb = fmaf(S[4 * r + 3], kk.w, pb); S[4 * r + 3] *= ww.w; ob = fmaf(S[4 * r + 3], qq.w, ob);
-                    za = fmaf(zz.x, qq.x, za); ka = fmaf(kk.x, qq.x, ka);
-                    zb = fmaf(zz.y, qq.y, zb); kb = fmaf(kk.y, qq.y, kb);
-                    za = fmaf(zz.z, qq.z, za); ka = fmaf(kk.z, qq.z, ka);
-                    zb = fmaf(zz.w, qq.w, zb); kb = fmaf(kk.w, qq.w, kb);
+                    const float4 ww = w4[r], kk = k4[r], qq = q4[r];
+                    p0 = fmaf(S[4 * r + 0], kk.x, p0); S[4 * r + 0] *= ww.x; a0 = fmaf(S[4 * r + 0], qq.x, a0);
+                    p1 = fmaf(S[4 * r + 1], kk.y, p1); S[4 * r + 1] *= ww.y; a1 = fmaf(S[4 * r + 1], qq.y, a1);
+                    p2 = fmaf(S[4 * r + 2], kk.z, p2); S[4 * r + 2] *= ww.z; a2 = fmaf(S[4 * r + 2], qq.z, a2);
+                    p3 = fmaf(S[4 * r + 3], kk.w, p3); S[4 * r + 3] *= ww.w; a3 = fmaf(S[4 * r + 3], qq.w, a3);
                 }
-                float p = pa + pb, o = oa + ob, zr = za + zb, kr = ka + kb;
+                float p = (p0 + p1) + (p2 + p3), o = (a0 + a1) + (a2 + a3);
 #pragma unroll
                 for (int step = 1; step < LANES; step <<= 1) {
                     p += __shfl_xor_sync(0xffffffffu, p, step);
                     o += __shfl_xor_sync(0xffffffffu, o, step);
-                    zr += __shfl_xor_sync(0xffffffffu, zr, step);
-                    kr += __shfl_xor_sync(0xffffffffu, kr, step);
                 }
                 const float val = vt[t];
-                o = fmaf(val, kr, fmaf(-p, zr, o));
+                o = fmaf(val, ct[t], fmaf(-p, bt[t], o));
 #pragma unroll
                 for (int r = 0; r < R / 4; ++r) {
                     const float4 kk = k4[r], zz = z4[r];
-                    S[4 * r + 0] = fmaf(kk.x, val, fmaf(-zz.x, p, S[4 * r + 0]));
-                    S[4 * r + 1] = fmaf(kk.y, val, fmaf(-zz.y, p, S[4 * r + 1]));
-                    S[4 * r + 2] = fmaf(kk.z, val, fmaf(-zz.z, p, S[4 * r + 2]));
-                    S[4 * r + 3] = fmaf(kk.w, val, fmaf(-zz.w, p, S[4 * r + 3]));
+                    S[4 * r + 0] = fmaf(-zz.x, p, fmaf(kk.x, val, S[4 * r + 0]));
+                    S[4 * r + 1] = fmaf(-zz.y, p, fmaf(kk.y, val, S[4 * r + 1]));
+                    S[4 * r + 2] = fmaf(-zz.z, p, fmaf(kk.z, val, S[4 * r + 2]));
+                    S[4 * r + 3] = fmaf(-zz.w, p, fmaf(kk.w, val, S[4 * r + 3]));
                 }
                 if (live && l == 0)
                     out[(size_t)(tok0 + b * TB + t) * (H * dv) + h * dv + col] = o;
@@ -537,6 +550,25 @@ __global__ void mean_of_normed_kernel(const T* __restrict__ a, const T* __restri
         const float y = to_float(b[base + i]) * ib * wb[i];
         out[base + i] = from_float<T>(0.5f * (x + y));
     }
+}
+
+// The same with a single head as wide as the row (one root mean square a token, the weight over
+// the row, sigmoid of a gate of type T): one block a token.
+template <typename T>
+__global__ void row_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ld_gate,
+                                const float* __restrict__ weight, T* __restrict__ out, int dv,
+                                float eps) {
+    __shared__ float scratch[33];
+    const int n = blockIdx.x;
+    const float* x = o + (size_t)n * dv;
+    pdl_wait();
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < dv; j += blockDim.x) ss = fmaf(x[j], x[j], ss);
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)dv + eps);
+    pdl_trigger();
+    for (int j = threadIdx.x; j < dv; j += blockDim.x)
+        out[(size_t)n * dv + j] = from_float<T>(
+            x[j] * inv * weight[j] * sigmoid_f(to_float(gate[(size_t)n * ld_gate + j])));
 }
 
 template <typename VT, int MODE, int COLS, int LANES>
@@ -677,8 +709,9 @@ DE_EXPORT int de_retention_prep(int dtype, const void* proj, int ld, const int* 
 }
 
 // v_dtype: the type of v (DE_F32 for the delta rule, whose values come from its own preparation).
-// mode 1: g [N, ldg] and beta [N, ldb] are used (the delta rule); 2: g (the decays w) and z
-// [N, ldz] (the generalized delta rule); 0: decay [H].  conv_taps > 1: the slots also keep the
+// mode 1: g [N, ldg] and beta [N, ldb] are used (the delta rule); 2: g (the decays w), z
+// [N, ldz] and in beta's place the heads' (z . r, k . r) [N, 2 H] (the generalized delta rule);
+// 0: decay [H].  conv_taps > 1: the slots also keep the
 // last conv_taps - 1 rows of the first conv_channels columns of conv_proj (of type conv_dtype,
 // row stride conv_ld) at conv_offset of their state row.
 DE_EXPORT int de_state_scan(int mode, int v_dtype, const float* q, int ldq, const float* k,
@@ -714,7 +747,8 @@ DE_EXPORT int de_state_scan(int mode, int v_dtype, const float* q, int ldq, cons
 
 DE_EXPORT int de_gdelta_prep(int dtype, const void* proj, int ld, int r_col, int k_col, int a_col,
                              const float* wl, const float* w0, const float* a_bias, float* rr,
-                             float* kk, float* ww, float* zz, int n, int H, int dk, void* stream) {
+                             float* kk, float* ww, float* zz, float* dots, int n, int H, int dk,
+                             void* stream) {
     if (n <= 0) return 0;
     if (H <= 0 || dk <= 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
@@ -722,9 +756,9 @@ DE_EXPORT int de_gdelta_prep(int dtype, const void* proj, int ld, int r_col, int
     if (dtype == DE_BF16)
         return de_launch(gdelta_prep_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s,
                          (const __nv_bfloat16*)proj, ld, r_col, k_col, a_col, wl, w0, a_bias, rr,
-                         kk, ww, zz, H, dk);
+                         kk, ww, zz, dots, H, dk);
     return de_launch(gdelta_prep_kernel<float>, dim3(n), dim3(threads), 0, s, (const float*)proj,
-                     ld, r_col, k_col, a_col, wl, w0, a_bias, rr, kk, ww, zz, H, dk);
+                     ld, r_col, k_col, a_col, wl, w0, a_bias, rr, kk, ww, zz, dots, H, dk);
 }
 
 DE_EXPORT int de_silu_rows(int dtype, const void* proj, int ld, float* out, int n, int cols,
@@ -746,6 +780,15 @@ DE_EXPORT int de_head_gate(int dtype, const float* o, const void* gate, int ld_g
                            int mode, void* stream) {
     if (n <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
+    if (mode == 2 && H == 1 && dv > 256) {
+        const int threads = dv >= 2048 ? 512 : 256;
+        if (dtype == DE_BF16)
+            return de_launch(row_gate_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s, o,
+                             (const __nv_bfloat16*)gate, ld_gate, weight, (__nv_bfloat16*)out, dv,
+                             eps);
+        return de_launch(row_gate_kernel<float>, dim3(n), dim3(threads), 0, s, o,
+                         (const float*)gate, ld_gate, weight, (float*)out, dv, eps);
+    }
     const int warps = 4;
     dim3 grid((n * H + warps - 1) / warps);
     if (dtype == DE_BF16)

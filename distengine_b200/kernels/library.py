@@ -45,7 +45,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
     },
     "linear_small": {
         "de_linear_small_max_rows": [],
-        "de_linear_small": [P, I, P, I, P, I, I, I, I, I, I, P],
+        "de_linear_small": [P, I, P, I, P, I, I, I, I, I, I, I, P],
         "de_linear_small_parts": [I],
         "de_linear_small_norm": [P, I, P, I, P, I, I, I, I, I, P, I, I, F, P, I, P, P, P],
     },
@@ -85,7 +85,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_retention_prep": [I, P, I, P, P, I, I, I, P, P, I, P],
         "de_state_scan": [I, I, P, I, P, I, P, I, P, I, P, I, P, I, P, P, L, P, P, P, P, I, I, I,
                           I, I, P, I, I, I, I, I, P],
-        "de_gdelta_prep": [I, P, I, I, I, I, P, P, P, P, P, P, P, I, I, I, P],
+        "de_gdelta_prep": [I, P, I, I, I, I, P, P, P, P, P, P, P, P, I, I, I, P],
         "de_silu_rows": [I, P, I, P, I, I, P],
         "de_head_gate": [I, P, P, I, P, P, I, I, I, F, I, P],
         "de_mean_of_normed": [I, P, P, P, P, P, I, I, F, P],

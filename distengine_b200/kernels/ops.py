@@ -378,8 +378,11 @@ def _tcgen05_fits(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> bool:
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
            out_dtype: "torch.dtype | None" = None,
-           status: "torch.Tensor | None" = None, before=None, after=None) -> torch.Tensor:
-    """x @ w^T, float32 accumulation.
+           status: "torch.Tensor | None" = None, before=None, after=None,
+           act: "str | None" = None) -> torch.Tensor:
+    """x @ w^T, float32 accumulation.  ``act`` (a key of ``ACTIVATIONS``): the activation that the
+    outputs pass, in the weight-streaming kernel's epilogue for steps of up to 16 tokens, as a
+    kernel of its own otherwise.
 
     ``before`` (``.parts`` float32 [rows, count], ``.width``, ``.eps``): x is the output of an RMS
     norm but for the rows' factors rsqrt(sum of the row's parts / width + eps), which the product
@@ -399,10 +402,14 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
         out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
     if x.shape[0] == 0:
         return out
+    _need(act is None or (act in ACTIVATIONS and before is None and after is None),
+          f"linear: act is one of {sorted(ACTIVATIONS)} and goes with no norm")
     if x.dtype == torch.float32:
         _need(out.dtype == torch.float32, "linear: a float32 product has a float32 output")
         _need(before is None and after is None, "linear: float32 products carry no norm")
         gemm_f32(x, w, out)
+        if act is not None:
+            activation(out, out, act)
         return out
     _need(x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16,
           "linear: operands must both be bfloat16 or both float32")
@@ -416,14 +423,18 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: "torch.Tensor | None" = None,
         lib = library.load("linear_small")
         _check(lib.de_linear_small(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0),
                                    out.data_ptr(), out.stride(0), x.shape[0], w.shape[0],
-                                   x.shape[1], int(out.dtype == torch.float32), 0, _stream()),
+                                   x.shape[1], int(out.dtype == torch.float32), 0,
+                                   0 if act is None else ACTIVATIONS[act] + 1, _stream()),
                "linear_small")
+        return out
     elif _tcgen05_fits(x, w, out):
         gemm_tcgen05(x, w, out, status=status)
     elif out.dtype == torch.bfloat16:
         torch.mm(x, w.t(), out=out)
     else:
         torch.mm(x, w.t(), out_dtype=torch.float32, out=out)
+    if act is not None:
+        activation(out, out, act)
     return out
 
 
@@ -464,7 +475,7 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor,
         lib = library.load("linear_small")
         _check(lib.de_linear_small(x.data_ptr(), x.stride(0), w_gate_up.data_ptr(),
                                    w_gate_up.stride(0), out.data_ptr(), out.stride(0), x.shape[0],
-                                   inner, x.shape[1], 0, 1, _stream()), "linear_small (gated)")
+                                   inner, x.shape[1], 0, 1, 0, _stream()), "linear_small (gated)")
         return out
     if not gated_needs_scratch(x, w_gate_up) and out.stride(1) == 1 and out.dtype == x.dtype:
         return gemm_tcgen05(x, w_gate_up, out, gated=True, status=status)

@@ -92,12 +92,13 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
                out: torch.Tensor, heads: int, qk_heads: int, key_dim: int, value_dim: int, ctx,
                g: "torch.Tensor | None" = None, beta: "torch.Tensor | None" = None,
                decay: "torch.Tensor | None" = None, keep: "tuple | None" = None,
-               z: "torch.Tensor | None" = None) -> None:
+               z: "torch.Tensor | None" = None, dots: "torch.Tensor | None" = None) -> None:
     """Walk every sequence's tokens of the step through its state ``state`` [slots, >= H dk dv]
     (float32, rows [h][key channel][value channel] at the front) and write the read-outs, float32
     [N, H dv].  With ``g`` [N, H dk] and ``beta`` [N, H]: the delta rule with a decay per key
-    channel.  With ``g`` and ``z`` [N, H dk]: the generalized delta rule, S <- diag(g) S -
-    z (k^T S) + k v^T with both first terms reading the old S.  With ``decay`` [H]: retention.
+    channel.  With ``g`` and ``z`` [N, H dk] and ``dots`` [N, 2 H] (every head's z . q and
+    k . q): the generalized delta rule, S <- diag(g) S - z (k^T S) + k v^T with both first terms
+    reading the old S.  With ``decay`` [H]: retention.
     q, k float32 [N, qk_heads dk]; v [N, H dv] in
     float32 or the activation dtype (any row stride).  ``keep`` = (proj, offset, channels, taps):
     the slots also keep, at ``offset`` of their rows, the last ``taps - 1`` rows of the first
@@ -123,9 +124,11 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
         _need(g.shape == (n, heads * key_dim) and beta.shape == (n, heads)
               and v.dtype == torch.float32, "state_scan: g [N, H dk], beta [N, H], v float32")
     elif general:
-        _f32(g, "g"), _f32(z, "z")
-        _need(g.shape == z.shape == (n, heads * key_dim) and qk_heads == heads,
-              "state_scan: g and z [N, H dk], one query/key head a head")
+        _f32(g, "g"), _f32(z, "z"), _f32(dots, "dots")
+        _need(g.shape == z.shape == (n, heads * key_dim) and qk_heads == heads
+              and dots.shape == (n, 2 * heads),
+              "state_scan: g and z [N, H dk], dots [N, 2 H], one query/key head a head")
+        beta = dots
     else:
         _f32(decay, "decay")
         _need(decay.shape == (heads,) and decay.is_contiguous(), "state_scan: decay [H]")
@@ -140,7 +143,7 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
     _check(lib.de_state_scan(2 if general else int(delta), _tag(v.dtype), q.data_ptr(),
                              q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0),
                              _ptr(g), g.stride(0) if g is not None else 0, _ptr(beta),
-                             beta.stride(0) if delta else 0, _ptr(z),
+                             beta.stride(0) if beta is not None else 0, _ptr(z),
                              z.stride(0) if general else 0, _ptr(decay), state.data_ptr(),
                              state.stride(0), out.data_ptr(), ctx.seq_slot.data_ptr(),
                              ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs, heads,
@@ -150,11 +153,14 @@ def state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
 
 def gdelta_prep(proj: torch.Tensor, r_col: int, k_col: int, a_col: int, wl: torch.Tensor,
                 w0: torch.Tensor, a_bias: torch.Tensor, rr: torch.Tensor, kk: torch.Tensor,
-                ww: torch.Tensor, zz: torch.Tensor, heads: int, key_dim: int) -> None:
+                ww: torch.Tensor, zz: torch.Tensor, dots: torch.Tensor, heads: int,
+                key_dim: int) -> None:
     """What the generalized delta rule needs of every token besides its values, all float32
     [N, H dk]: r and k as they stand in ``proj`` (from columns ``r_col`` and ``k_col``), the
     decays w = exp(-exp(-1/2) sigmoid(wl + w0)) from the low-rank projection ``wl`` (float32), and
-    z = sigmoid(a + a_bias) k / (|k|^2 + 1e-6) per head with a from column ``a_col``."""
+    z = sigmoid(a + a_bias) k / (|k|^2 + 1e-6) per head with a from column ``a_col``; and
+    ``dots`` float32 [N, 2 H]: every head's (z . r, k . r), which ``state_scan`` takes as
+    ``dots``."""
     n, hk = proj.shape[0], heads * key_dim
     _need(proj.stride(1) == 1 and proj.shape[1] >= max(r_col, k_col, a_col) + hk,
           "gdelta_prep: proj is too narrow")
@@ -165,11 +171,14 @@ def gdelta_prep(proj: torch.Tensor, r_col: int, k_col: int, a_col: int, wl: torc
     for t, name in ((w0, "w0"), (a_bias, "a_bias")):
         _f32(t, name)
         _need(tuple(t.shape) == (hk,) and t.is_contiguous(), f"gdelta_prep: {name} [H dk]")
+    _f32(dots, "dots")
+    _need(tuple(dots.shape) == (n, 2 * heads) and dots.is_contiguous(),
+          "gdelta_prep: dots must be contiguous [N, 2 H]")
     lib = library.load("recurrent")
     _check(lib.de_gdelta_prep(_tag(proj.dtype), proj.data_ptr(), proj.stride(0), r_col, k_col,
                               a_col, wl.data_ptr(), w0.data_ptr(), a_bias.data_ptr(),
-                              rr.data_ptr(), kk.data_ptr(), ww.data_ptr(), zz.data_ptr(), n, heads,
-                              key_dim, _stream()), "gdelta_prep")
+                              rr.data_ptr(), kk.data_ptr(), ww.data_ptr(), zz.data_ptr(),
+                              dots.data_ptr(), n, heads, key_dim, _stream()), "gdelta_prep")
 
 
 def silu_rows(proj: torch.Tensor, out: torch.Tensor) -> None:

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..config.model import LayerSpec, ModelConfig
-from ..kernels import ops
+from ..kernels import library, ops
 from ..parts.base import (Block, PagedKVSpec, StateSpec, build_block, build_feed_forward,
                           build_mixer, build_norm, compute_matrix)
 from ..parts.context import CacheBinding, ResidualStream, StepContext, StepPrep
@@ -66,7 +66,20 @@ class DecoderModel:
         optional = {names["output"]} if self.config.tied_output else set()
         return expected, vectors, optional
 
+    def kernel_modules(self) -> "list[tuple[str, tuple]]":
+        """The kernel libraries every step of this model uses: the row-wise kernels, the product
+        of its dtype for steps of few tokens, and what its parts name."""
+        modules = ["core", "gemm_f32" if self.dtype == torch.float32 else "linear_small"]
+        for block in self.blocks:
+            for part in block.parts().values():
+                for module in part.kernel_modules():
+                    if module not in modules:
+                        modules.append(module)
+        return [(module, ()) for module in modules]
+
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        if self.device.type == "cuda":
+            library.preload(self.kernel_modules())       # compiled side by side, if not yet
         names = self.config.tensor_names()
         self.embedding = compute_matrix(tensors[names["embedding"]], self.dtype, self.device)
         for spec, block in zip(self.specs, self.blocks):

@@ -79,6 +79,12 @@ class Part:
         """Called once per step before the step's arrays go to the device: a part may add int32
         arrays of its own (work lists) with ``prep.add``."""
 
+    def kernel_modules(self) -> "tuple[str, ...]":
+        """The kernel libraries (``kernels.build.MODULES``) that this part's steps are sure to
+        use, besides the products': the model compiles them side by side when it is loaded
+        instead of one after the other at their first use."""
+        return ()
+
 
 class Norm(Part):
     def forward(self, stream: ResidualStream, ctx: StepContext,

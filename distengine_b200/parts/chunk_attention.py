@@ -60,6 +60,9 @@ class ChunkAttention(ProjectedMixer):
     def input_matrix(self) -> torch.Tensor:
         return self._host_in
 
+    def kernel_modules(self):
+        return ("attention_chunk",)
+
     def cache_spec(self):
         return PagedKVSpec(self.kv_heads, self.dk, None, value_dim=self.dv, chunk=self.chunk)
 

@@ -89,8 +89,7 @@ class DenseMLP(FeedForward):
     def forward(self, x: torch.Tensor, ctx: StepContext, ahead=None) -> torch.Tensor:
         n = x.shape[0]
         act = ctx.buffer("mlp.act", (n, self.inner))
-        ops.linear(x, self.w_up, out=act, status=ctx.status)
-        ops.activation(act, act, self.activation)
+        ops.linear(x, self.w_up, out=act, status=ctx.status, act=self.activation)
         out = ctx.buffer("mlp.out", (n, self.width))
         ops.linear(act, self.w_down, out=out, status=ctx.status)
         return out

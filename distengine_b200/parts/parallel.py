@@ -75,6 +75,10 @@ class ParallelMixer(Mixer):
     def cache_spec(self):
         return tuple(branch.cache_spec() for branch in self.branches)
 
+    def kernel_modules(self):
+        own = ("recurrent",) if self.combine == "mean_of_normed" else ()
+        return tuple(m for branch in self.branches for m in branch.kernel_modules()) + own
+
     def prepare(self, prep: StepPrep) -> None:
         for branch in self.branches:
             branch.prepare(prep)

@@ -79,6 +79,9 @@ class ProjectedMixer(Mixer):
 
     w_in: "torch.Tensor | None" = None
 
+    def kernel_modules(self):
+        return ("recurrent",)
+
     def input_matrix(self) -> torch.Tensor:
         raise NotImplementedError
 
@@ -332,10 +335,12 @@ class GeneralizedDeltaRule(ProjectedMixer):
         kk = ctx.buffer("gdelta.k", (n, rows), f32)
         ww = ctx.buffer("gdelta.w", (n, rows), f32)
         zz = ctx.buffer("gdelta.z", (n, rows), f32)
-        rk.gdelta_prep(proj, 0, rows, 4 * rows, wl, self.w0, self.a_bias, rr, kk, ww, zz, H, dk)
+        dots = ctx.buffer("gdelta.dots", (n, 2 * H), f32)
+        rk.gdelta_prep(proj, 0, rows, 4 * rows, wl, self.w0, self.a_bias, rr, kk, ww, zz, dots,
+                       H, dk)
         o = ctx.buffer("gdelta.o", (n, rows), f32)
         rk.state_scan(rr, kk, proj[:, 2 * rows: 3 * rows], cache.state, o, H, H, dk, dk, ctx,
-                      g=ww, z=zz)
+                      g=ww, z=zz, dots=dots)
         gated = ctx.buffer("gdelta.gated", (n, rows))
         rk.head_gate(o, proj[:, 3 * rows: 4 * rows], self.norm, gated, H, dk, self.eps,
                      spanning=True)

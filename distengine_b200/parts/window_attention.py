@@ -112,6 +112,9 @@ class WindowAttention(ProjectedMixer):
     def input_matrix(self) -> torch.Tensor:
         return self._host_in
 
+    def kernel_modules(self):
+        return ("attention_chunk",)
+
     def cache_spec(self):
         return PagedKVSpec(self.kv_heads, self.dk, self.cache_window, value_dim=self.dv,
                            keep_first=self.cache_keep_first if self.cache_window else 0)

@@ -117,11 +117,14 @@ def test_generalized_delta_rule_scan_carries_its_state(H, dk):
         def cut(fn):
             return torch.cat([fn(*(t[fed[s]: fed[s] + pieces[s]] for t in data[s]))
                               .reshape(pieces[s], -1) for s in range(2)]).to(DEV).contiguous()
-        z = cut(lambda r, k, v, w, a: a * k / ((k * k).sum(-1, keepdim=True) + 1e-6))
+        zf = lambda r, k, v, w, a: a * k / ((k * k).sum(-1, keepdim=True) + 1e-6)
+        z = cut(zf)
+        dots = cut(lambda r, k, v, w, a: torch.stack(((zf(r, k, v, w, a) * r).sum(-1),
+                                                      (k * r).sum(-1)), dim=-1))
         out = torch.empty(sum(pieces), H * dk, device=DEV)
         rk.state_scan(cut(lambda r, k, v, w, a: r), cut(lambda r, k, v, w, a: k),
                       cut(lambda r, k, v, w, a: v), state, out, H, H, dk, dk, ctx,
-                      g=cut(lambda r, k, v, w, a: w), z=z)
+                      g=cut(lambda r, k, v, w, a: w), z=z, dots=dots)
         at = 0
         for s in range(2):
             got[s][fed[s]: fed[s] + pieces[s]] = out[at: at + pieces[s]].cpu().view(-1, H, dk)
@@ -154,8 +157,9 @@ def test_generalized_delta_rule_removes_along_the_unit_key():
     state = torch.zeros(1, H * dk * dk, device=DEV)
     out = torch.empty(3, H * dk, device=DEV)
     z = ones * k / ((k * k).sum(-1, keepdim=True) + 1e-6)
+    dots = torch.stack(((z * r).sum(-1), (k * r).sum(-1)), dim=-1)
     rk.state_scan(flat(r), flat(k), flat(v), state, out, H, H, dk, dk, ctx, g=flat(ones),
-                  z=flat(z))
+                  z=flat(z), dots=flat(dots))
     assert_close(out.view(3, H, dk), want, torch.float32, "removal along the unit key")
 
 
@@ -169,8 +173,9 @@ def test_generalized_delta_preparation(dtype):
     wl = torch.randn(n, rows, generator=g) * 2
     w0, a_bias = torch.randn(rows, generator=g), torch.randn(rows, generator=g)
     outs = [torch.empty(n, rows, device=DEV) for _ in range(4)]
+    dots = torch.empty(n, 2 * H, device=DEV)
     rk.gdelta_prep(proj.to(DEV), 0, rows, 4 * rows, wl.to(DEV), w0.to(DEV), a_bias.to(DEV),
-                   *outs, H, dk)
+                   *outs, dots, H, dk)
     p = proj.double()
     k = p[:, rows: 2 * rows].view(n, H, dk)
     a = torch.sigmoid(p[:, 4 * rows: 5 * rows] + a_bias.double()).view(n, H, dk)
@@ -179,8 +184,11 @@ def test_generalized_delta_preparation(dtype):
     assert_close(outs[2], torch.exp(-np.exp(-0.5) * torch.sigmoid(wl.double() + w0.double())),
                  torch.float32, "decay")
     # (a u)(u^T S) with the unit key u = k / sqrt(|k|^2 + 1e-6) is z (k^T S)
-    assert_close(outs[3], (a * k / ((k * k).sum(-1, keepdim=True) + 1e-6)).reshape(n, rows),
-                 torch.float32, "z")
+    z = a * k / ((k * k).sum(-1, keepdim=True) + 1e-6)
+    assert_close(outs[3], z.reshape(n, rows), torch.float32, "z")
+    r = p[:, :rows].view(n, H, dk)
+    assert_close(dots.view(n, H, 2), torch.stack(((z * r).sum(-1), (k * r).sum(-1)), dim=-1),
+                 torch.float32, "z . r and k . r")
 
 
 def test_lightning_state_keeps_a_far_token():
