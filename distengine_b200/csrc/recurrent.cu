@@ -259,7 +259,9 @@ __device__ __forceinline__ int state_row(int r, int l) {      // register r of s
 
 // MODE 0: retention; 1: the delta rule (g, beta); 2: the generalized delta rule (g = w, z).
 template <typename VT, int R, int MODE, int COLS, int LANES>
-__global__ void __launch_bounds__(COLS * LANES, (MODE == 2 && R <= 32) ? 384 / (COLS * LANES) : 1)
+// (the generalized rule at 32 columns is held to three blocks an SM: single tokens stream the
+// states, and 183 registers a thread would leave two)
+__global__ void __launch_bounds__(COLS * LANES, (MODE == 2 && R <= 32 && COLS == 32) ? 3 : 1)
 scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
             const VT* __restrict__ v, int ldv, const float* __restrict__ g, int ldg,
             const float* __restrict__ beta, int ldb, const float* __restrict__ z, int ldz,
