@@ -498,7 +498,8 @@ def vomotar_kernels(peak: dict) -> list[dict]:
         aproj = torch.randn(n, AH * dk + G * (dk + dv), device=dev).to(bf16)
         us = timed(lambda: rk.kv_write_normed(aproj, AH * dk, G, dk, dv, 1e-5, kp, vp, table, ctx))
         record("kv_write_normed", case, us, bytes_=n * G * (dk + dv) * 4)
-        rows = rk.chunk_rows_per_tile(bf16, dk, dv, n > s)
+        rows = rk.chunk_rows_per_tile(bf16, dk, dv, n > s,
+                                      rk.long_portion_rows(ctx.host.seq_qlen, AH, G))
         plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, AH // G, G, rows, 0, chunk=0)
         items = torch.from_numpy(plan.items).to(dev)
         ao = torch.empty(n, AH * dv, dtype=bf16, device=dev)
@@ -701,7 +702,8 @@ def sebilorn_kernels(peak: dict) -> list[dict]:
                                                True, ctx))
         record("kv_write_rotated", case, us, bytes_=n * (2 * H * dk + 2 * G * (dk + dv)) * 2,
                like="kv_write_normed")
-        rows = rk.chunk_rows_per_tile(bf16, dk, dv, n > s)
+        rows = rk.chunk_rows_per_tile(bf16, dk, dv, n > s,
+                                      rk.long_portion_rows(ctx.host.seq_qlen, H, G))
         plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H // G, G, rows, 0, chunk=0)
         items = torch.from_numpy(plan.items).to(dev)
         raw = torch.empty(n, H * dv, device=dev)

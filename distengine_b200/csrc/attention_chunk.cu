@@ -595,6 +595,259 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ 
 
 
 // ------------------------------------------------------------------------------------------
+// The same attention for long prompt portions, with the products tiled in registers: a block of
+// four warps takes 64 rows, a warp 16 of them against the tile of 32 keys.  Lane (i, j) of a warp
+// (i = lane / 8, j = lane % 8) holds rows i, i + 4, i + 8, i + 12 against keys j, j + 8, j + 16,
+// j + 24: a step over four features is four 16-byte reads of q and four of k from shared memory
+// for 64 multiply-adds (the kernel above: five reads for 16), and rows and keys that meet in one
+// read lie 4 banks apart.  The weights go through shared memory once ([key][row], a warp's own
+// 2 KB), and for the values lane (i, j) holds the same four rows against columns 4 j + 32 c.
+// A row's score sums its features in ascending order, a row's sums over a tile's keys have an
+// order of their own (fixed by the key's place in its tile), so a row's result does not depend on
+// what shares its tile, its step or its batch.  Sizes as the kernel above.
+// ------------------------------------------------------------------------------------------
+constexpr int TROWS = 64;
+
+template <typename T, int NC>
+__global__ void __launch_bounds__(128, NC <= 4 ? 3 : 2)
+attn_chunk_tiled_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ out,
+                        int out_stride, const T* __restrict__ k_pages,
+                        const T* __restrict__ v_pages, const int* __restrict__ block_table,
+                        int table_stride, int num_pages, const int* __restrict__ seq_slot,
+                        const int* __restrict__ seq_qstart, const int* __restrict__ seq_qlen,
+                        const int* __restrict__ seq_pos0, const WorkItem* __restrict__ items,
+                        const float* __restrict__ r1, const float* __restrict__ r2, int heads,
+                        int kv_heads, int dk, int dv, int page, float scale, Sight sight,
+                        int out_f32, int* __restrict__ status) {
+    constexpr int PN = Piece<T>::N;
+    extern __shared__ __align__(16) float smem[];
+    const int kst = dk + 4;                          // a key's and a query's stride
+    float* Ks = smem;                                // [TILE][kst]
+    float* Vs = Ks + TILE * kst;                     // [TILE][dv]
+    float* Qs = Vs + TILE * dv;                      // [TROWS][kst]
+    float* Ps = Qs + TROWS * kst;                    // [4 warps][TILE][16]
+    float* Held = Ps + 4 * TILE * 16;                // [TILE]: 0, or -inf for a key without a page
+
+    const WorkItem it = items[blockIdx.x];
+    if (it.kv_begin >= it.kv_end) {
+        pdl_wait();
+        return;
+    }
+    const int hk = blockIdx.y;
+    const int g = heads / kv_heads;
+    const int qlen = seq_qlen[it.seq], pos0 = seq_pos0[it.seq];
+    const int slot = seq_slot[it.seq], tok0 = seq_qstart[it.seq];
+    const int rows_total = qlen * g;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int li = lane >> 3, lj = lane & 7;
+    const bool penalty = r1 != nullptr;
+
+    bool active[4];
+    int tok[4], hq[4], pos[4], row_lo[4], row_hi[4], row_first[4];
+    float pen1[4], pen2[4], m[4], l[4];
+    bool mine = false;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const int r = it.row0 + warp * 16 + li + 4 * e;
+        active[e] = r < rows_total;
+        mine |= active[e];
+        tok[e] = active[e] ? r / g : 0;
+        hq[e] = hk * g + (active[e] ? r % g : 0);
+        pos[e] = pos0 + tok[e];
+        pen1[e] = penalty ? r1[hq[e]] : 0.0f;
+        pen2[e] = penalty ? r2[hq[e]] : 0.0f;
+        row_lo[e] = max(it.kv_begin, sight_lo(sight, pos[e]));
+        row_first[e] = it.kv_begin > 0 ? 0 : sight_first(sight, row_lo[e]);
+        row_hi[e] = min(it.kv_end, pos[e] + 1);
+        m[e] = -INFINITY;
+        l[e] = 0.0f;
+    }
+    const bool any = __any_sync(0xffffffffu, mine);
+    const int last_row = min(it.row0 + TROWS, rows_total) - 1;
+    const int max_pos = pos0 + last_row / g, min_pos = pos0 + it.row0 / g;
+    const int k_hi = min(it.kv_end, max_pos + 1);
+    const int k_lo_true = max(it.kv_begin, sight_lo(sight, min_pos));
+    const int k_first = it.kv_begin > 0 ? 0 : sight_first(sight, k_lo_true);
+    const TileWalk walk(k_lo_true, k_first, TILE);
+    const int ck = dk / PN, cv = dv / PN, per_key = ck + cv;
+
+    pdl_wait();
+    for (int idx = threadIdx.x; idx < TROWS * dk; idx += 128) {
+        const int row = idx / dk, d = idx - row * dk;
+        const int r = it.row0 + row;
+        float x = 0.0f;
+        if (r < rows_total)
+            x = to_float(q[(size_t)(tok0 + r / g) * q_stride + (hk * g + r % g) * dk + d]);
+        Qs[row * kst + d] = x;
+    }
+
+    float acc[4][NC][4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[e][c][x] = 0.0f;
+
+    float* Pw = Ps + warp * TILE * 16;
+    for (int kt = walk.start; kt < k_hi; kt = walk.next(kt, TILE)) {
+        __syncthreads();                             // the tile before this one has been used
+        for (int e0 = 0; e0 < TILE * per_key; e0 += 4 * 128) {
+            uint4 piece[4];
+            bool gone[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {            // four loads in flight a thread
+                const int e = e0 + u * 128 + threadIdx.x;
+                piece[u] = make_uint4(0u, 0u, 0u, 0u);
+                gone[u] = false;
+                if (e >= TILE * per_key) continue;
+                const int j = e / per_key, w = e - j * per_key;
+                const int kpos = kt + j;
+                if ((kpos < k_lo_true && kpos >= k_first) || kpos >= k_hi) continue;
+                const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
+                if (page_id < 0 || page_id >= num_pages) {
+                    gone[u] = true;
+                    continue;
+                }
+                const size_t at = ((size_t)page_id * kv_heads + hk) * page + (size_t)(kpos % page);
+                const T* src = w < ck ? k_pages + at * dk + w * PN
+                                      : v_pages + at * dv + (w - ck) * PN;
+                piece[u] = *reinterpret_cast<const uint4*>(src);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int e = e0 + u * 128 + threadIdx.x;
+                if (e >= TILE * per_key) continue;
+                const int j = e / per_key, w = e - j * per_key;
+                float f[PN];
+                Piece<T>::unpack(piece[u], f);
+                float* dst = w < ck ? Ks + j * kst + w * PN : Vs + j * dv + (w - ck) * PN;
+#pragma unroll
+                for (int x = 0; x < PN; x += 4)
+                    *reinterpret_cast<float4*>(dst + x) =
+                        make_float4(f[x], f[x + 1], f[x + 2], f[x + 3]);
+                if (w == 0) {
+                    Held[j] = gone[u] ? -INFINITY : 0.0f;
+                    if (gone[u] && status != nullptr) atomicExch(status, 2);
+                }
+            }
+        }
+        __syncthreads();
+        if (!any) continue;
+
+        float s[4][4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[e][c] = 0.0f;
+        const float* qb = Qs + (warp * 16 + li) * kst;
+        const float* kb = Ks + lj * kst;
+#pragma unroll 2
+        for (int d = 0; d < dk; d += 4) {
+            float4 qv[4], kv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) qv[e] = *reinterpret_cast<const float4*>(qb + 4 * e * kst + d);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) kv[c] = *reinterpret_cast<const float4*>(kb + 8 * c * kst + d);
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    s[e][c] = fmaf(qv[e].x, kv[c].x, s[e][c]);
+                    s[e][c] = fmaf(qv[e].y, kv[c].y, s[e][c]);
+                    s[e][c] = fmaf(qv[e].z, kv[c].z, s[e][c]);
+                    s[e][c] = fmaf(qv[e].w, kv[c].w, s[e][c]);
+                }
+        }
+        bool held[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) held[c] = Held[lj + 8 * c] == 0.0f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            float top = -INFINITY;
+            bool valid[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int kpos = kt + lj + 8 * c;
+                valid[c] = active[e] && (kpos >= row_lo[e] || kpos < row_first[e]) &&
+                           kpos < row_hi[e] && held[c];
+                s[e][c] = valid[c] ? sight_score(sight, s[e][c], scale, pen1[e], pen2[e], penalty,
+                                                 (float)(pos[e] - kpos))
+                                   : -INFINITY;
+                top = fmaxf(top, s[e][c]);
+            }
+            top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+            top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+            top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 4));
+            const float m_new = fmaxf(m[e], top);
+            float sum = 0.0f, corr = 1.0f;
+            if (m_new == -INFINITY) {                // nothing of this tile is visible to the row
+#pragma unroll
+                for (int c = 0; c < 4; ++c) s[e][c] = 0.0f;
+            } else {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    s[e][c] = valid[c] ? expf(s[e][c] - m_new) : 0.0f;
+                    sum += s[e][c];
+                }
+                corr = expf(m[e] - m_new);
+                m[e] = m_new;
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            l[e] = l[e] * corr + sum;
+#pragma unroll
+            for (int c = 0; c < NC; ++c)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) acc[e][c][x] *= corr;
+        }
+        __syncwarp();                                // the weights of the tile before have been read
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<float4*>(Pw + (lj + 8 * c) * 16 + 4 * li) =
+                make_float4(s[0][c], s[1][c], s[2][c], s[3][c]);
+        __syncwarp();
+#pragma unroll 4
+        for (int key = 0; key < TILE; ++key) {
+            const float4 pv = *reinterpret_cast<const float4*>(Pw + key * 16 + 4 * li);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const int col = 4 * lj + 32 * c;
+                if (col < dv) {
+                    const float4 vv = *reinterpret_cast<const float4*>(Vs + key * dv + col);
+                    acc[0][c][0] = fmaf(pv.x, vv.x, acc[0][c][0]); acc[0][c][1] = fmaf(pv.x, vv.y, acc[0][c][1]);
+                    acc[0][c][2] = fmaf(pv.x, vv.z, acc[0][c][2]); acc[0][c][3] = fmaf(pv.x, vv.w, acc[0][c][3]);
+                    acc[1][c][0] = fmaf(pv.y, vv.x, acc[1][c][0]); acc[1][c][1] = fmaf(pv.y, vv.y, acc[1][c][1]);
+                    acc[1][c][2] = fmaf(pv.y, vv.z, acc[1][c][2]); acc[1][c][3] = fmaf(pv.y, vv.w, acc[1][c][3]);
+                    acc[2][c][0] = fmaf(pv.z, vv.x, acc[2][c][0]); acc[2][c][1] = fmaf(pv.z, vv.y, acc[2][c][1]);
+                    acc[2][c][2] = fmaf(pv.z, vv.z, acc[2][c][2]); acc[2][c][3] = fmaf(pv.z, vv.w, acc[2][c][3]);
+                    acc[3][c][0] = fmaf(pv.w, vv.x, acc[3][c][0]); acc[3][c][1] = fmaf(pv.w, vv.y, acc[3][c][1]);
+                    acc[3][c][2] = fmaf(pv.w, vv.z, acc[3][c][2]); acc[3][c][3] = fmaf(pv.w, vv.w, acc[3][c][3]);
+                }
+            }
+        }
+    }
+    pdl_trigger();
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        if (!active[e]) continue;
+        const float inv = l[e] > 0.0f ? 1.0f / l[e] : 0.0f;
+        const size_t o = (size_t)(tok0 + tok[e]) * out_stride + hq[e] * dv;
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+            const int col = 4 * lj + 32 * c;
+            if (col < dv) {
+#pragma unroll
+                for (int x = 0; x < 4; ++x)
+                    store_out<T>(out, out_f32, o + col + x, acc[e][c][x] * inv);
+            }
+        }
+    }
+}
+
+
+// ------------------------------------------------------------------------------------------
 // Steps in which every sequence brings one token.  A block takes a sequence and a kv head; its
 // eight warps share the key tiles of the token's chunk out among themselves (warp w takes tiles
 // w, w + 8, ...) and each works alone: it asks for its tile's 32 key rows and 32 value rows at
@@ -808,8 +1061,16 @@ static bool vec_ok(int dtype, int dk, int dv) {
     const int pn = dtype == DE_BF16 ? 8 : 4;
     return dk % pn == 0 && dv % pn == 0 && dk <= MAX_D && dv <= MAX_D;
 }
+static size_t tiled_smem(int dk, int dv) {
+    return (size_t)(TILE * (dk + 4) + TILE * dv + TROWS * (dk + 4) + 4 * TILE * 16 + TILE) *
+           sizeof(float);
+}
+// `wide`: 0 for steps of single tokens, else the rows (tokens times query heads a kv head) of the
+// step's longest portion (1: some portion): from 48 rows on the register-tiled kernel's 64.
 DE_EXPORT int de_attn_chunk_rows(int dtype, int dk, int dv, int wide) {
-    return vec_ok(dtype, dk, dv) && wide ? ROWS * 4 : ROWS;
+    if (!(vec_ok(dtype, dk, dv) && wide)) return ROWS;
+    if (wide >= 48 && tiled_smem(dk, dv) <= 200 * 1024) return TROWS;
+    return ROWS * 4;
 }
 
 static size_t decode_smem(int dtype, int rw, int dk, int dv) {
@@ -939,7 +1200,40 @@ DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, i
     const Sight sight = {chunk, window, keep_first, softcap};
     if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D || heads % kv_heads != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
-    if (tile_rows != ROWS && !(tile_rows == ROWS * 4 && vec_ok(dtype, dk, dv))) return -5;
+    if (tile_rows != ROWS && !((tile_rows == ROWS * 4 || tile_rows == TROWS) && vec_ok(dtype, dk, dv)))
+        return -5;
+    if (tile_rows == TROWS) {
+        if ((uintptr_t)k_pages % 16 != 0 || (uintptr_t)v_pages % 16 != 0) return -5;
+        const size_t tsmem = tiled_smem(dk, dv);
+        if (tsmem > 200 * 1024) return -5;
+        const int nc = (dv + 31) / 32;
+        dim3 tgrid(num_items, kv_heads);
+#define TILED(T, NC)                                                                            \
+    do {                                                                                        \
+        if (tsmem > 48 * 1024) {                                                                \
+            cudaError_t te = cudaFuncSetAttribute(attn_chunk_tiled_kernel<T, NC>,               \
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                                  (int)tsmem);                                  \
+            if (te != cudaSuccess) return (int)te;                                              \
+        }                                                                                       \
+        return de_launch(attn_chunk_tiled_kernel<T, NC>, tgrid, dim3(128), tsmem, s,            \
+                         (const T*)q, q_stride, out, out_stride, (const T*)k_pages,             \
+                         (const T*)v_pages, block_table, table_stride, num_pages, seq_slot,     \
+                         seq_qstart, seq_qlen, seq_pos0, (const WorkItem*)items, r1, r2, heads, \
+                         kv_heads, dk, dv, page, scale, sight, out_f32, status);                \
+    } while (0)
+#define TILED_N(T)                                                                              \
+    do {                                                                                        \
+        if (nc <= 1) TILED(T, 1);                                                               \
+        if (nc <= 2) TILED(T, 2);                                                               \
+        if (nc <= 4) TILED(T, 4);                                                               \
+        TILED(T, 8);                                                                            \
+    } while (0)
+        if (dtype == DE_BF16) TILED_N(__nv_bfloat16);
+        TILED_N(float);
+#undef TILED_N
+#undef TILED
+    }
     if (vec_ok(dtype, dk, dv) && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0) {
         const int rw = tile_rows / ROWS;
         const int pn = dtype == DE_BF16 ? 8 : 4;

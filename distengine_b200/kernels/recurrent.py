@@ -243,11 +243,31 @@ def _penalty(r1, r2, heads: int) -> None:
         _need(r1.shape == r2.shape == (heads,), "attention: r1, r2 [heads]")
 
 
-def chunk_rows_per_tile(dtype: torch.dtype, key_dim: int, value_dim: int, wide: bool) -> int:
+def chunk_rows_per_tile(dtype: torch.dtype, key_dim: int, value_dim: int, wide: bool,
+                        longest_rows: int = 0) -> int:
     """Rows of a tile of the chunk attention: 8, or 32 for steps with prompt portions (``wide``)
-    at sizes whose rows are whole 16-byte pieces."""
+    at sizes whose rows are whole 16-byte pieces, or 64 where the longest portion has at least 48
+    rows (``longest_rows``: its tokens times the query heads a kv head)."""
+    hint = max(int(wide), int(longest_rows)) if wide else 0
     return int(library.load("attention_chunk").de_attn_chunk_rows(_tag(dtype), key_dim, value_dim,
-                                                                  int(wide)))
+                                                                  hint))
+
+
+_sm_count: dict[int, int] = {}
+
+
+def long_portion_rows(seq_qlen, heads: int, kv_heads: int) -> int:
+    """The rows of a step's longest portion (tokens times query heads a kv head) if tiles of 64
+    rows would still give every SM two blocks, else 0: what ``chunk_rows_per_tile`` takes as
+    ``longest_rows``.  (Measured on B200, 16 heads on 4 kv heads of 128: a prompt of 512 tokens
+    takes 311 us in 128 blocks of 64 rows against 221 us in 256 blocks of 32; one of 2,048 tokens
+    838 against 1,362 us.)"""
+    group = heads // kv_heads
+    device = torch.cuda.current_device()
+    if device not in _sm_count:
+        _sm_count[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    blocks = int(((seq_qlen.astype("int64") * group + 63) // 64).sum()) * kv_heads
+    return int(seq_qlen.max()) * group if blocks >= 2 * _sm_count[device] else 0
 
 
 def chunk_decode_ok(dtype: torch.dtype, heads: int, kv_heads: int, key_dim: int,

@@ -85,7 +85,8 @@ class ChunkAttention(ProjectedMixer):
             return
         # tiles of 32 rows when the step brings prompt portions, of 8 for single tokens
         rows = rk.chunk_rows_per_tile(self.dtype, self.dk, self.dv,
-                                      int(host.seq_qlen.max()) > 1)
+                                      int(host.seq_qlen.max()) > 1,
+                                      rk.long_portion_rows(host.seq_qlen, self.heads, self.kv_heads))
         plan = build_plan(host.seq_qlen, host.seq_pos0, self.heads // self.kv_heads,
                           self.kv_heads, rows, 0, chunk=0)
         prep.add(name, plan.items)

@@ -137,7 +137,8 @@ class WindowAttention(ProjectedMixer):
             prep.notes[self.key] = 0
             return
         rows = rk.chunk_rows_per_tile(self.dtype, self.dk, self.dv,
-                                      int(host.seq_qlen.max()) > 1)
+                                      int(host.seq_qlen.max()) > 1,
+                                      rk.long_portion_rows(host.seq_qlen, self.heads, self.kv_heads))
         plan = build_plan(host.seq_qlen, host.seq_pos0, self.heads // self.kv_heads,
                           self.kv_heads, rows, 0, chunk=0)
         prep.add(name, plan.items)

@@ -91,9 +91,24 @@ SEBI_C = {
     ],
 }
 
-ALL = {"sebi_a": SEBI_A, "sebi_b": SEBI_B, "sebi_c": SEBI_C}
-SEEDS = {"sebi_a": 15, "sebi_b": 16, "sebi_c": 17}
-PAGES = {"sebi_a": 16, "sebi_b": 8, "sebi_c": 16}
+# many heads of whole 16-byte rows: a prompt of a thousand tokens has so many rows that the
+# attention takes tiles of 64 rows and the products a thousand rows and more
+SEBI_WIDE = {
+    "architecture": "Sebilorn", "vocab": 300, "width": 256, "norm": {"eps": 1e-6},
+    "embedding": {"scale": 4.0}, "logit_softcap": 30.0,
+    "layers": [
+        _attention(24, 4, 32, 32, 0.18, 300, 5, _rot(32, 250000.0, (4.0, 1.0, 4.0, 256)), 20.0,
+                   ff=512),
+        _parallel((24, 4, 32, 16, 0.18, _rot(16, 10000.0)), (4, 64, 16), (0.6, 0.5), 512),
+        _attention(24, 4, 32, 32, 0.18, 1000, 0, _rot(32, 250000.0, (4.0, 1.0, 4.0, 256)), None,
+                   0),
+        _lightning(4, 32, 64, [0.9, 0.99, 0.999, 0.97]),
+    ],
+}
+
+ALL = {"sebi_a": SEBI_A, "sebi_b": SEBI_B, "sebi_c": SEBI_C, "sebi_wide": SEBI_WIDE}
+SEEDS = {"sebi_a": 15, "sebi_b": 16, "sebi_c": 17, "sebi_wide": 18}
+PAGES = {"sebi_a": 16, "sebi_b": 8, "sebi_c": 16, "sebi_wide": 16}
 
 
 def write_folder(config: dict, folder: str, weights: dict) -> str:

@@ -125,6 +125,35 @@ def test_long_decoding_with_graphs(name, dtype_name, model_root):
         _compare(rows, {"long": want}, DTYPES[dtype_name], f"long decode graphs={graphs}")
 
 
+@pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
+def test_a_long_prompt_at_wide_sizes(dtype_name, model_root):
+    """1,100 tokens in one step (products of a thousand rows and more, attention tiles of 64 rows,
+    windows of 300 and 1,000 keys passing), then tokens one by one, then the same prompt in two
+    uneven portions."""
+    from distengine_b200.engine.replay import build_runner
+    from distengine_b200.kernels import recurrent as rk
+    name = "sebi_wide"
+    folder, weights = sc.make_folder(name, model_root)
+    ids = sc.tokens(name, 1112, 3)
+    assert rk.long_portion_rows(np.array([1100], dtype=np.int32), 24, 4) >= 48
+    act = None if dtype_name == "float32" else torch.bfloat16
+    want = ps.forward(sc.ALL[name], weights, ids, act=act).to(torch.float32).numpy()
+    picked = [0, 1, 4, 5, 299, 300, 301, 304, 305, 306, 599, 999, 1000, 1001, 1099]
+    head = {"step": 0, "end": [], "entries": [{"id": "w", "tokens": ids[:1100], "want": picked}]}
+    tail = [{"step": 1 + i, "end": ["w"] if i == 11 else [],
+             "entries": [{"id": "w", "tokens": [ids[1100 + i]], "want": [0]}]} for i in range(12)]
+    cut = [{"step": 13, "end": [], "entries": [{"id": "c", "tokens": ids[:1027], "want": [1026]}]},
+           {"step": 14, "end": ["c"], "entries": [{"id": "c", "tokens": ids[1027:],
+                                                    "want": [0, 84]}]}]
+    steps = [head] + tail + cut
+    runner = build_runner(folder, dtype_name, 1152, page_size=16, poison_freed_pages=True)
+    with tempfile.TemporaryDirectory() as out:
+        th.replay_in_process(runner, steps, out)
+        rows = th.collect(steps, out, sc.ALL[name]["vocab"])
+    assert len(rows) == len(picked) + 12 + 3
+    _compare(rows, {"w": want, "c": want}, DTYPES[dtype_name], f"wide {dtype_name}")
+
+
 def test_pages_behind_a_window_come_back_but_the_first_stay(model_root):
     """After 200 tokens the windowed groups hold the pages of their kept first tokens and of the
     window only; the group that sees everything holds all."""

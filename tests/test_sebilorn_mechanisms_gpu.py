@@ -288,7 +288,8 @@ def _attend(q, k, v, pages, pieces_list, H, G, dk, dv, dtype, rot, fk, fv, scale
                                       dk, dv, scale, 0, ctx, window=window, keep_first=keep,
                                       softcap=softcap)
         else:
-            tile = rk.chunk_rows_per_tile(dtype, dk, dv, max(pieces) > 1)
+            # (tiles of 64 rows from 48 rows a portion on, whatever the step's number of blocks)
+            tile = rk.chunk_rows_per_tile(dtype, dk, dv, max(pieces) > 1, max(pieces) * (H // G))
             plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H // G, G, tile, 0, chunk=0)
             items = torch.from_numpy(plan.items).to(DEV)
             rk.chunk_attention(proj, raw, pages.k, pages.v, pages.table, items, None, None, H, G,
@@ -327,8 +328,10 @@ def _plain_attention(q, k, v, dtype, fk, fv, scale, window, keep, softcap, gate=
 
 
 # (H, G, dk, dv, page): odd sizes take the general kernel; whole 16-byte rows the one that loads
-# them so and, for single tokens, the one that takes a (sequence, kv head) a block
-SHAPES = [(4, 2, 10, 6, 8), (8, 1, 32, 64, 16), (3, 3, 24, 16, 4), (16, 1, 16, 8, 16)]
+# them so, from 48 rows a portion on the one that tiles its products in registers and, for single
+# tokens, the one that takes a (sequence, kv head) a block
+SHAPES = [(4, 2, 10, 6, 8), (8, 1, 32, 64, 16), (3, 3, 24, 16, 4), (16, 1, 16, 8, 16),
+          (4, 2, 128, 128, 16), (2, 1, 40, 200, 8)]
 
 
 @pytest.mark.parametrize("H,G,dk,dv,page", SHAPES)
