@@ -692,44 +692,50 @@ attn_chunk_tiled_kernel(const T* __restrict__ q, int q_stride, void* __restrict_
     float* Pw = Ps + warp * TILE * 16;
     for (int kt = walk.start; kt < k_hi; kt = walk.next(kt, TILE)) {
         __syncthreads();                             // the tile before this one has been used
-        for (int e0 = 0; e0 < TILE * per_key; e0 += 4 * 128) {
-            uint4 piece[4];
-            bool gone[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {            // four loads in flight a thread
-                const int e = e0 + u * 128 + threadIdx.x;
-                piece[u] = make_uint4(0u, 0u, 0u, 0u);
-                gone[u] = false;
-                if (e >= TILE * per_key) continue;
-                const int j = e / per_key, w = e - j * per_key;
-                const int kpos = kt + j;
-                if ((kpos < k_lo_true && kpos >= k_first) || kpos >= k_hi) continue;
+        {
+            // four threads a key: thread t takes the key's 16-byte pieces t % 4, t % 4 + 4, ...
+            // (keys first, then values), so its key, its page and its row are found once a tile
+            const int j = threadIdx.x >> 2, w0 = threadIdx.x & 3;
+            const int kpos = kt + j;
+            const bool inside = (kpos >= k_lo_true || kpos < k_first) && kpos < k_hi;
+            bool gone = false;
+            size_t at = 0;
+            if (inside) {
                 const int page_id = block_table[(size_t)slot * table_stride + kpos / page];
-                if (page_id < 0 || page_id >= num_pages) {
-                    gone[u] = true;
-                    continue;
-                }
-                const size_t at = ((size_t)page_id * kv_heads + hk) * page + (size_t)(kpos % page);
-                const T* src = w < ck ? k_pages + at * dk + w * PN
-                                      : v_pages + at * dv + (w - ck) * PN;
-                piece[u] = *reinterpret_cast<const uint4*>(src);
+                gone = page_id < 0 || page_id >= num_pages;
+                at = ((size_t)page_id * kv_heads + hk) * page + (size_t)(kpos % page);
             }
+            const bool read = inside && !gone;
+            const T* ksrc = k_pages + at * dk;
+            const T* vsrc = v_pages + at * dv;
+            float* kdst = Ks + j * kst;
+            float* vdst = Vs + j * dv;
+            for (int w = w0; w < per_key; w += 16) {
+                uint4 piece[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int e = e0 + u * 128 + threadIdx.x;
-                if (e >= TILE * per_key) continue;
-                const int j = e / per_key, w = e - j * per_key;
-                float f[PN];
-                Piece<T>::unpack(piece[u], f);
-                float* dst = w < ck ? Ks + j * kst + w * PN : Vs + j * dv + (w - ck) * PN;
-#pragma unroll
-                for (int x = 0; x < PN; x += 4)
-                    *reinterpret_cast<float4*>(dst + x) =
-                        make_float4(f[x], f[x + 1], f[x + 2], f[x + 3]);
-                if (w == 0) {
-                    Held[j] = gone[u] ? -INFINITY : 0.0f;
-                    if (gone[u] && status != nullptr) atomicExch(status, 2);
+                for (int u = 0; u < 4; ++u) {        // four loads in flight a thread
+                    const int ww = w + 4 * u;
+                    piece[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (read && ww < per_key)
+                        piece[u] = *reinterpret_cast<const uint4*>(
+                            ww < ck ? ksrc + ww * PN : vsrc + (ww - ck) * PN);
                 }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int ww = w + 4 * u;
+                    if (ww >= per_key) continue;
+                    float f[PN];
+                    Piece<T>::unpack(piece[u], f);
+                    float* dst = ww < ck ? kdst + ww * PN : vdst + (ww - ck) * PN;
+#pragma unroll
+                    for (int x = 0; x < PN; x += 4)
+                        *reinterpret_cast<float4*>(dst + x) =
+                            make_float4(f[x], f[x + 1], f[x + 2], f[x + 3]);
+                }
+            }
+            if (w0 == 0) {
+                Held[j] = gone ? -INFINITY : 0.0f;
+                if (gone && status != nullptr) atomicExch(status, 2);
             }
         }
         __syncthreads();
@@ -808,14 +814,15 @@ attn_chunk_tiled_kernel(const T* __restrict__ q, int q_stride, void* __restrict_
             *reinterpret_cast<float4*>(Pw + (lj + 8 * c) * 16 + 4 * li) =
                 make_float4(s[0][c], s[1][c], s[2][c], s[3][c]);
         __syncwarp();
+        const float* vrow = Vs + 4 * lj;
+        const float* prow = Pw + 4 * li;
 #pragma unroll 4
-        for (int key = 0; key < TILE; ++key) {
-            const float4 pv = *reinterpret_cast<const float4*>(Pw + key * 16 + 4 * li);
+        for (int key = 0; key < TILE; ++key, vrow += dv, prow += 16) {
+            const float4 pv = *reinterpret_cast<const float4*>(prow);
 #pragma unroll
             for (int c = 0; c < NC; ++c) {
-                const int col = 4 * lj + 32 * c;
-                if (col < dv) {
-                    const float4 vv = *reinterpret_cast<const float4*>(Vs + key * dv + col);
+                if (4 * lj + 32 * c < dv) {
+                    const float4 vv = *reinterpret_cast<const float4*>(vrow + 32 * c);
                     acc[0][c][0] = fmaf(pv.x, vv.x, acc[0][c][0]); acc[0][c][1] = fmaf(pv.x, vv.y, acc[0][c][1]);
                     acc[0][c][2] = fmaf(pv.x, vv.z, acc[0][c][2]); acc[0][c][3] = fmaf(pv.x, vv.w, acc[0][c][3]);
                     acc[1][c][0] = fmaf(pv.y, vv.x, acc[1][c][0]); acc[1][c][1] = fmaf(pv.y, vv.y, acc[1][c][1]);

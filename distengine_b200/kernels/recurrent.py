@@ -260,8 +260,8 @@ def long_portion_rows(seq_qlen, heads: int, kv_heads: int) -> int:
     """The rows of a step's longest portion (tokens times query heads a kv head) if tiles of 64
     rows would still give every SM two blocks, else 0: what ``chunk_rows_per_tile`` takes as
     ``longest_rows``.  (Measured on B200, 16 heads on 4 kv heads of 128: a prompt of 512 tokens
-    takes 311 us in 128 blocks of 64 rows against 221 us in 256 blocks of 32; one of 2,048 tokens
-    838 against 1,362 us.)"""
+    takes 274 us in 128 blocks of 64 rows against 221 us in 256 blocks of 32; one of 2,048 tokens
+    739 against 1,362 us.)"""
     group = heads // kv_heads
     device = torch.cuda.current_device()
     if device not in _sm_count:
