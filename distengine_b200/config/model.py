@@ -132,3 +132,27 @@ def positive(name: str, value: int) -> int:
     if value <= 0:
         raise ConfigError(f"config.json: '{name}' must be positive, got {value}")
     return value
+
+
+# ----------------------------------------------------------------------------- nested keys
+# Readers for configurations whose keys are nested: ``where`` is the path of the object that holds
+# the key ("layers[2].mixer."), so that an error names the whole path.
+def section(data: Mapping[str, Any], key: str, where: str) -> Mapping[str, Any]:
+    value = data.get(key)
+    if not isinstance(value, Mapping):
+        raise ConfigError(f"config.json: {where}'{key}' must be an object")
+    return value
+
+
+def positive_int(data: Mapping[str, Any], key: str, where: str) -> int:
+    try:
+        return positive(where + key, require(data, key, int))
+    except ConfigError as error:
+        raise ConfigError(str(error).replace(f"'{key}'", f"'{where}{key}'")) from None
+
+
+def number(data: Mapping[str, Any], key: str, where: str) -> float:
+    value = data.get(key)
+    if isinstance(value, bool) or not isinstance(value, (int, float)):
+        raise ConfigError(f"config.json: '{where}{key}' must be a number, got {value!r}")
+    return float(value)

@@ -29,8 +29,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Mapping
 
-from .model import ConfigError, LayerSpec, ModelConfig, PartSpec, PlanEntry, positive, require
-from .vomotar import _int, _number, _section
+from .model import (ConfigError, LayerSpec, ModelConfig, PartSpec, PlanEntry, positive, require,
+                    number as _number, positive_int as _int, section as _section)
 
 NAME = "Sebilorn"
 MAX_POSITIONS = 1 << 20          # the design names none; positions are exact in float32 far beyond

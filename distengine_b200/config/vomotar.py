@@ -23,31 +23,11 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Mapping
 
-from .model import ConfigError, LayerSpec, ModelConfig, PartSpec, positive, require
+from .model import (ConfigError, LayerSpec, ModelConfig, PartSpec, positive, require,
+                    number as _number, positive_int as _int, section as _section)
 
 NAME = "Vomotar"
 MAX_POSITIONS = 1 << 20          # the design names none; positions are exact in float32 far beyond
-
-
-def _section(data: Mapping[str, Any], key: str, where: str) -> Mapping[str, Any]:
-    value = data.get(key)
-    if not isinstance(value, Mapping):
-        raise ConfigError(f"config.json: {where}'{key}' must be an object")
-    return value
-
-
-def _int(data: Mapping[str, Any], key: str, where: str) -> int:
-    try:
-        return positive(where + key, require(data, key, int))
-    except ConfigError as error:
-        raise ConfigError(str(error).replace(f"'{key}'", f"'{where}{key}'")) from None
-
-
-def _number(data: Mapping[str, Any], key: str, where: str) -> float:
-    value = data.get(key)
-    if isinstance(value, bool) or not isinstance(value, (int, float)):
-        raise ConfigError(f"config.json: '{where}{key}' must be a number, got {value!r}")
-    return float(value)
 
 
 def _delta(m: Mapping[str, Any], where: str) -> tuple:
