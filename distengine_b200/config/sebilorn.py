@@ -7,8 +7,9 @@ The file names every size and every constant that differs between models of the 
      "layers": [{"type": "attention" | "parallel" | "lightning", "mixer": {...},
                  "mlp": {"kind": "dense", "ff": F} | null}, ...]}
 
-* ``attention`` mixer: ``heads``, ``kv_heads``, ``dim``, ``vdim``, ``scale``, ``softcap``,
-  ``mask`` (``size`` of the sliding window, ``keep_first`` tokens that stay visible), ``rot``
+* ``attention`` mixer: ``heads``, ``kv_heads``, ``dim``, ``vdim`` (where absent: ``dim``),
+  ``scale``, ``softcap`` (optional), ``mask`` (``size`` of the sliding window, ``keep_first``
+  tokens that stay visible; without a mask every earlier token is seen), ``rot``
   (``dims``, ``base``, optional ``scaling`` with ``factor``, ``low``, ``high``, ``original``), and
   optionally ``kv_from``: the index of the earlier layer whose keys and values it reads instead of
   having matrices of its own.  Values are rotated by position and the heads' results turned back.
@@ -65,14 +66,18 @@ def _heads(m: Mapping[str, Any], where: str) -> tuple[int, int]:
 
 def _attention(m: Mapping[str, Any], where: str, index: int) -> dict:
     heads, kv_heads = _heads(m, where)
-    dim, vdim = _int(m, "dim", where), _int(m, "vdim", where)
+    dim = _int(m, "dim", where)
+    vdim = _int(m, "vdim", where) if m.get("vdim") is not None else dim
     if vdim % 2:
         raise ConfigError(f"config.json: '{where}vdim' ({vdim}) must be even: values are rotated "
                           f"in pairs")
-    mask = _section(m, "mask", where)
-    keep = mask.get("keep_first", 0)
-    if type(keep) is not int or keep < 0:
-        raise ConfigError(f"config.json: '{where}mask.keep_first' must be an integer >= 0")
+    window, keep = None, 0                           # no mask: every earlier token is seen
+    if m.get("mask") is not None:
+        mask = _section(m, "mask", where)
+        keep = mask.get("keep_first", 0)
+        if type(keep) is not int or keep < 0:
+            raise ConfigError(f"config.json: '{where}mask.keep_first' must be an integer >= 0")
+        window = _int(mask, "size", where + "mask.")
     softcap = m.get("softcap")
     if softcap is not None:
         softcap = _number(m, "softcap", where)
@@ -83,7 +88,7 @@ def _attention(m: Mapping[str, Any], where: str, index: int) -> dict:
         raise ConfigError(f"config.json: '{where}kv_from' ({kv_from!r}) must name an earlier layer")
     return {"kind": "attention", "heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
             "scale": _number(m, "scale", where), "softcap": softcap,
-            "window": _int(mask, "size", where + "mask."), "keep_first": keep,
+            "window": window, "keep_first": keep,
             "rot": _rotation(m, where, dim), "kv_from": kv_from}
 
 
@@ -97,7 +102,8 @@ def _parallel(m: Mapping[str, Any], where: str) -> dict:
         raise ConfigError(f"config.json: '{wb}rank' must be a positive integer")
     return {"kind": "parallel",
             "left": {"heads": heads, "kv_heads": kv_heads, "dim": dim,
-                     "vdim": _int(a, "vdim", wa), "scale": _number(a, "scale", wa),
+                     "vdim": _int(a, "vdim", wa) if a.get("vdim") is not None else dim,
+                     "scale": _number(a, "scale", wa),
                      "rot": _rotation(a, wa, dim)},
             "right": {"heads": _int(b, "heads", wb), "dim": _int(b, "dim", wb), "rank": rank},
             "left_scale": _number(m, "left_scale", where),
@@ -111,8 +117,10 @@ def _lightning(m: Mapping[str, Any], where: str) -> dict:
             or any(isinstance(x, bool) or not isinstance(x, (int, float)) for x in decay)):
         raise ConfigError(f"config.json: '{where}decay' must list one number for each of the "
                           f"{heads} heads")
-    return {"kind": "lightning", "heads": heads, "dim": _int(m, "dim", where),
-            "vdim": _int(m, "vdim", where), "decay": tuple(float(x) for x in decay)}
+    dim = _int(m, "dim", where)
+    return {"kind": "lightning", "heads": heads, "dim": dim,
+            "vdim": _int(m, "vdim", where) if m.get("vdim") is not None else dim,
+            "decay": tuple(float(x) for x in decay)}
 
 
 def _freeze(value):
@@ -210,9 +218,9 @@ class SebilornConfig(ModelConfig):
             if m["kind"] == "attention":
                 mixer: dict[str, Any] = {
                     "heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"],
-                    "vdim": m["vdim"], "scale": m["scale"],
-                    "mask": {"size": m["window"], "keep_first": m["keep_first"]},
-                    "rot": _rot_json(m["rot"])}
+                    "vdim": m["vdim"], "scale": m["scale"], "rot": _rot_json(m["rot"])}
+                if m["window"] is not None:
+                    mixer["mask"] = {"size": m["window"], "keep_first": m["keep_first"]}
                 if m["softcap"] is not None:
                     mixer["softcap"] = m["softcap"]
                 if m["kv_from"] is not None:
@@ -283,7 +291,9 @@ class SebilornConfig(ModelConfig):
         for i, m in enumerate(mixers):
             if m["kind"] == "attention" and m["kv_from"] is not None:
                 j = m["kv_from"]
-                window[j], kept[j] = max(window[j], m["window"]), max(kept[j], m["keep_first"])
+                both = window[j] is not None and m["window"] is not None
+                window[j] = max(window[j], m["window"]) if both else None
+                kept[j] = max(kept[j], m["keep_first"])
         for i, (m, (_, ff)) in enumerate(zip(mixers, self.layers)):
             base = f"l{i}."
             if m["kind"] == "attention":

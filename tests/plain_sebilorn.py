@@ -126,7 +126,8 @@ def window_attention_mixer(h, w, pre, m, eps, act=None, shared=None):
     fv = frequencies(rot["base"], dv, None, h.dtype)
     q = rnd(rotate(lin(h, w[pre + "q"], act).reshape(T, H, dk), positions, fq), act)
     kv = shared if shared is not None else attention_keys_values(h, w, pre, m, positions, act)
-    see = visible(T, m["mask"]["size"], m["mask"]["keep_first"])
+    mask = m.get("mask") or {}                         # no mask: every earlier token is seen
+    see = visible(T, mask.get("size"), mask.get("keep_first", 0))
     o = softmax_attention(q, kv[0], kv[1], m["scale"], see, m.get("softcap"))
     o = rnd(rotate(o, positions, fv, sign=-1.0), act)        # every head's sum turned back
     return lin(o.reshape(T, H * dv), w[pre + "o"], act), kv

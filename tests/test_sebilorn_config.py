@@ -92,6 +92,17 @@ def test_defaults_where_the_file_is_silent():
     assert full.embedding_scale == 3.0 and full.logit_softcap == 9.0
 
 
+def test_an_attention_layer_without_a_mask_sees_everything():
+    config = copy.deepcopy(sc.SEBI_C)
+    del config["layers"][2]["mixer"]["mask"]             # a reader of layer 0 without a window
+    del config["layers"][3]["mixer"]["vdim"]
+    arch, parsed = resolve(config)
+    assert resolve(parsed.to_json())[1] == parsed
+    specs = arch.build_model(parsed, torch.float32, "meta").cache_specs()
+    assert specs[0] == PagedKVSpec(1, 32, None, value_dim=64)       # nothing may be given back
+    assert specs[3].value_dim == 16
+
+
 def test_the_pages_of_kept_first_tokens_are_never_given_back():
     spec = PagedKVSpec(2, 8, window=20, value_dim=4, keep_first=9)
     plain = PagedKVSpec(2, 8, window=20, value_dim=4)

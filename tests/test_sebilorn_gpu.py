@@ -225,6 +225,8 @@ def _random_config(rng) -> dict:
                                         int(pick(1, 3, 16, 17, 64, 300)), int(pick(0, 1, 7, 33)),
                                         sc._rot(dims, float(pick(50.0, 10000.0)), scaling),
                                         pick(None, 4.0, 30.0), None, ff))
+            if rng.random() < 0.2:
+                del layers[-1]["mixer"]["mask"]          # every earlier token is seen
             owners.append(i)
         elif kind == "parallel":
             kv = int(pick(1, 2))
