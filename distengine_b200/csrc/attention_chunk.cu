@@ -869,16 +869,32 @@ __device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src) : "memory");
 }
 
+// What the kernel for single tokens does besides the attention when `on`: it turns its token's
+// queries by position (in shared memory), turns and stores the token's key and value of its kv
+// head in the pages before it reads them (write_kv; q's row is then [q (H dk) | k (G dk) |
+// v (G dv) | ...]), and it finishes every head's result itself - turned back by position where fv
+// is given, times sigmoid(gate) where a gate is given, rounded to T - as kv_write_rotated and
+// attn_finish_kernel do around the other kernels, with the same arithmetic.
+struct Fuse {
+    int on;
+    const float* fk;
+    int rot;
+    const float* fv;
+    int write_kv;
+    const void* gate;
+    int ld_gate;
+};
+
 template <typename T, int RW>
 __global__ void __launch_bounds__(ROWS * 32)
 attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ out,
-                         int out_stride, const T* __restrict__ k_pages,
-                         const T* __restrict__ v_pages, const int* __restrict__ block_table,
+                         int out_stride, T* k_pages, T* v_pages,
+                         const int* __restrict__ block_table,
                          int table_stride, int num_pages, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_qstart, const int* __restrict__ seq_pos0,
                          const float* __restrict__ r1, const float* __restrict__ r2, int heads,
                          int kv_heads, int dk, int dv, int page, float scale, Sight sight,
-                         int out_f32, int* __restrict__ status) {
+                         int out_f32, Fuse fuse, int* __restrict__ status) {
     constexpr int PN = Piece<T>::N;
     extern __shared__ __align__(16) float smem[];
     float* Qs = smem;                                // [RW][dk]
@@ -917,6 +933,58 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
         Qs[e] = i < g ? to_float(q[(size_t)tok * q_stride + (hk * g + i) * dk + d]) : 0.0f;
     }
     __syncthreads();
+    if (fuse.on) {
+        const float fpos = (float)pos;
+        const int half = fuse.rot / 2;
+        for (int e = threadIdx.x; e < g * half; e += ROWS * 32) {
+            const int i = e / half, p = e - i * half;
+            float sn, cs, ra, rb;
+            sincosf(fpos * fuse.fk[p], &sn, &cs);
+            rope_rotate(Qs[i * dk + p], Qs[i * dk + p + half], cs, sn, ra, rb);
+            Qs[i * dk + p] = to_float(from_float<T>(ra));        // rounded as when q goes through memory
+            Qs[i * dk + p + half] = to_float(from_float<T>(rb));
+        }
+        if (fuse.write_kv) {
+            const int page_id = block_table[(size_t)slot * table_stride + pos / page];
+            if (page_id < 0 || page_id >= num_pages) {           // never written outside the pool
+                if (threadIdx.x == 0 && status != nullptr) atomicExch(status, 1);
+            } else {
+                const size_t at = ((size_t)page_id * kv_heads + hk) * page + (size_t)(pos % page);
+                const T* ks = q + (size_t)tok * q_stride + heads * dk + hk * dk;
+                const T* vs = q + (size_t)tok * q_stride + (heads + kv_heads) * dk + hk * dv;
+                T* kd = k_pages + at * dk;
+                T* vd = v_pages + at * dv;
+                for (int i = threadIdx.x; i < dk - half; i += ROWS * 32) {
+                    if (i < half) {
+                        float sn, cs, ra, rb;
+                        sincosf(fpos * fuse.fk[i], &sn, &cs);
+                        rope_rotate(to_float(ks[i]), to_float(ks[i + half]), cs, sn, ra, rb);
+                        kd[i] = from_float<T>(ra);
+                        kd[i + half] = from_float<T>(rb);
+                    } else {
+                        kd[i + half] = ks[i + half];
+                    }
+                }
+                if (fuse.fv != nullptr) {
+                    const int vhalf = dv / 2;
+                    for (int i = threadIdx.x; i < dv - vhalf; i += ROWS * 32) {
+                        if (i < vhalf) {
+                            float sn, cs, ra, rb;
+                            sincosf(fpos * fuse.fv[i], &sn, &cs);
+                            rope_rotate(to_float(vs[i]), to_float(vs[i + vhalf]), cs, sn, ra, rb);
+                            vd[i] = from_float<T>(ra);
+                            vd[i + vhalf] = from_float<T>(rb);
+                        } else {
+                            vd[i + vhalf] = vs[i + vhalf];
+                        }
+                    }
+                } else {
+                    for (int i = threadIdx.x; i < dv; i += ROWS * 32) vd[i] = vs[i];
+                }
+            }
+        }
+        __syncthreads();                             // the block reads what it has just stored
+    }
     float acc[RW][MAX_D / 32];
 #pragma unroll
     for (int i = 0; i < RW; ++i)
@@ -1052,6 +1120,38 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
         }
         const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
         const size_t o = (size_t)tok * out_stride + (hk * g + i) * dv;
+        if (fuse.on) {
+            // the head's result through shared memory (the place of the first warp's share of
+            // this head, which only this warp reads), so that a lane finds its feature's pair
+            float* fin = Pacc + (size_t)i * dv;
+            __syncwarp();
+#pragma unroll
+            for (int b = 0; b < MAX_D / 32; ++b) {
+                const int dd = lane + 32 * b;
+                if (dd < dv) fin[dd] = res[b] * inv;
+            }
+            __syncwarp();
+            const int vhalf = dv / 2;
+            const T* gt = fuse.gate
+                              ? (const T*)fuse.gate + (size_t)tok * fuse.ld_gate + (hk * g + i) * dv
+                              : nullptr;
+#pragma unroll
+            for (int b = 0; b < MAX_D / 32; ++b) {
+                const int dd = lane + 32 * b;
+                if (dd >= dv) continue;
+                float x = fin[dd];
+                if (fuse.fv != nullptr && dd < 2 * vhalf) {
+                    const int p = dd < vhalf ? dd : dd - vhalf;
+                    float sn, cs, ra, rb;
+                    sincosf((float)pos * fuse.fv[p], &sn, &cs);
+                    rope_rotate(fin[p], fin[p + vhalf], cs, -sn, ra, rb);
+                    x = dd < vhalf ? ra : rb;
+                }
+                if (gt) x *= 1.0f / (1.0f + expf(-to_float(gt[dd])));
+                ((T*)out)[o + dd] = from_float<T>(x);
+            }
+            continue;
+        }
 #pragma unroll
         for (int b = 0; b < MAX_D / 32; ++b) {
             const int dd = lane + 32 * b;
@@ -1097,15 +1197,19 @@ DE_EXPORT int de_attn_chunk_decode_ok(int dtype, int heads, int kv_heads, int dk
 }
 
 DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void* out,
-                                   int out_stride, const void* k_pages, const void* v_pages,
+                                   int out_stride, void* k_pages, void* v_pages,
                                    const int* block_table, int table_stride, int num_pages,
                                    const int* seq_slot, const int* seq_qstart,
                                    const int* seq_pos0, int n_seqs, const float* r1,
                                    const float* r2, int heads, int kv_heads, int dk, int dv,
                                    int page, float scale, int chunk, int window, int keep_first,
-                                   float softcap, int out_f32, int* status, void* stream) {
+                                   float softcap, int out_f32, int fused, const float* fk, int rot,
+                                   const float* fv, int write_kv, const void* gate, int ld_gate,
+                                   int* status, void* stream) {
     if (n_seqs <= 0) return 0;
     const Sight sight = {chunk, window, keep_first, softcap};
+    const Fuse fuse = {fused, fk, rot, fv, write_kv, gate, ld_gate};
+    if (fused && (rot < 0 || rot % 2 || rot > dk || (fv != nullptr && dv % 2) || out_f32)) return -2;
     if (!de_attn_chunk_decode_ok(dtype, heads, kv_heads, dk, dv) || (uintptr_t)k_pages % 16 != 0)
         return -2;
     cudaStream_t s = (cudaStream_t)stream;
@@ -1123,10 +1227,10 @@ DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void*
             if (e != cudaSuccess) return (int)e;                                                \
         }                                                                                       \
         return de_launch(attn_chunk_decode_kernel<T, RW>, grid, dim3(ROWS * 32), smem, s,       \
-                         (const T*)q, q_stride, out, out_stride, (const T*)k_pages,             \
-                         (const T*)v_pages, block_table, table_stride, num_pages, seq_slot,     \
-                         seq_qstart, seq_pos0, r1, r2, heads, kv_heads, dk, dv, page, scale,    \
-                         sight, out_f32, status);                                               \
+                         (const T*)q, q_stride, out, out_stride, (T*)k_pages, (T*)v_pages,      \
+                         block_table, table_stride, num_pages, seq_slot, seq_qstart, seq_pos0,  \
+                         r1, r2, heads, kv_heads, dk, dv, page, scale, sight, out_f32, fuse,    \
+                         status);                                                               \
     } while (0)
 #define DEC_T(T)                                                                                \
     do {                                                                                        \

@@ -281,15 +281,42 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                            v_pages: torch.Tensor, block_table: torch.Tensor, r1: torch.Tensor,
                            r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
                            value_dim: int, scale: float, chunk: int, ctx, window: int = 0,
-                           keep_first: int = 0, softcap: float = 0.0) -> None:
+                           keep_first: int = 0, softcap: float = 0.0,
+                           fused: "dict | None" = None) -> None:
     """``chunk_attention`` for a step in which every sequence brings one token: a block a
-    (sequence, kv head), its warps share the key tiles out; no work items."""
+    (sequence, kv head), its warps share the key tiles out; no work items.
+
+    ``fused`` = {fk, rotary_dim, fv, write_kv, gate}: the kernel also does what
+    ``kv_write_rotated`` and ``attention_finish`` do around the other kernels - it turns the
+    queries (in its own memory: ``q`` stays as it is), turns and stores the token's key and value
+    (``q``'s rows are then [q (H dk) | k (G dk) | v (G dv) | ...]), turns every head's result back
+    and gates it; ``out`` has the activation dtype."""
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == k_pages.dtype
           and out.dtype in (q.dtype, torch.float32)
           and out.shape[1] == heads * value_dim and q.shape[0] == ctx.n_seqs,
           "chunk_attention_decode: q, out and pages; one token a sequence")
     _i32(block_table, "block_table")
     _penalty(r1, r2, heads)
+    extra = (0, None, 0, None, 0, None, 0)
+    if fused is not None:
+        fk, rot, fv, gate = fused["fk"], fused["rotary_dim"], fused["fv"], fused["gate"]
+        write_kv = bool(fused["write_kv"])
+        need = heads * key_dim + (kv_heads * (key_dim + value_dim) if write_kv else 0)
+        _need(out.dtype == q.dtype and q.shape[1] >= need, "chunk_attention_decode: fused steps "
+              "write the activation dtype and find k and v behind q")
+        _f32(fk, "fk")
+        _need(rot % 2 == 0 and 0 <= rot <= key_dim and fk.shape == (rot // 2,),
+              "chunk_attention_decode: fk [rotary_dim / 2]")
+        if fv is not None:
+            _f32(fv, "fv")
+            _need(value_dim % 2 == 0 and fv.shape == (value_dim // 2,),
+                  "chunk_attention_decode: fv [dv / 2]")
+        if gate is not None:
+            _need(gate.dtype == out.dtype and gate.stride(1) == 1
+                  and gate.shape == (q.shape[0], heads * value_dim),
+                  "chunk_attention_decode: gate [N, H dv] of out's dtype")
+        extra = (1, fk.data_ptr(), rot, _ptr(fv), int(write_kv), _ptr(gate),
+                 gate.stride(0) if gate is not None else 0)
     lib = library.load("attention_chunk")
     _check(lib.de_attn_chunk_decode(_tag(q.dtype), q.data_ptr(), q.stride(0), out.data_ptr(),
                                     out.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
@@ -300,7 +327,7 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                                     key_dim, value_dim, k_pages.shape[2], float(scale),
                                     int(chunk), int(window), int(keep_first), float(softcap),
                                     int(out.dtype == torch.float32 and q.dtype != torch.float32),
-                                    ctx.status.data_ptr(), _stream()),
+                                    *extra, ctx.status.data_ptr(), _stream()),
            "chunk_attention_decode")
 
 

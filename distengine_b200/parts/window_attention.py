@@ -151,23 +151,30 @@ class WindowAttention(ProjectedMixer):
             raise ValueError("window attention: a layer with key and value matrices writes its "
                              "own cache, one without reads another run's")
         n, H, dv = proj.shape[0], self.heads, self.dv
+        context = ctx.buffer("window_attention.context", (n, H * dv))
+        if ctx.notes[self.key] == 0:
+            # single tokens only: rotation, cache write, attention, back-rotation and gate are
+            # one kernel
+            gate = proj[:, self.g_col: self.g_col + H * dv] if self.gated else None
+            rk.chunk_attention_decode(
+                proj, context, cache.k_pages, cache.v_pages, cache.block_table, None, None, H,
+                self.kv_heads, self.dk, dv, self.scale, 0, ctx, window=self.window or 0,
+                keep_first=self.keep_first if self.window else 0, softcap=self.softcap or 0.0,
+                fused=dict(fk=self.fk, rotary_dim=self.rotary_dim, fv=self.fv,
+                           write_kv=cache.writes, gate=gate))
+            return self.project_out(context, "window_attention.out", ctx, ahead,
+                                    out_dtype=out_dtype)
         rk.kv_write_rotated(proj, self.fk, self.rotary_dim, self.fv, H, self.kv_heads, self.dk,
                             dv, cache.k_pages, cache.v_pages, cache.block_table, cache.writes, ctx)
         finish = self.fv is not None or self.gated
-        context = ctx.buffer("window_attention.context", (n, H * dv))
         raw = (ctx.buffer("window_attention.raw", (n, H * dv), torch.float32) if finish
                else context)
         sight = dict(window=self.window or 0, keep_first=self.keep_first if self.window else 0,
                      softcap=self.softcap or 0.0)
-        if ctx.notes[self.key] == 0:
-            rk.chunk_attention_decode(proj, raw, cache.k_pages, cache.v_pages, cache.block_table,
-                                      None, None, H, self.kv_heads, self.dk, dv, self.scale, 0,
-                                      ctx, **sight)
-        else:
-            rk.chunk_attention(proj, raw, cache.k_pages, cache.v_pages, cache.block_table,
-                               ctx.arrays[self.key + "/items"], None, None, H, self.kv_heads,
-                               self.dk, dv, self.scale, 0, ctx, tile_rows=ctx.notes[self.key],
-                               **sight)
+        rk.chunk_attention(proj, raw, cache.k_pages, cache.v_pages, cache.block_table,
+                           ctx.arrays[self.key + "/items"], None, None, H, self.kv_heads,
+                           self.dk, dv, self.scale, 0, ctx, tile_rows=ctx.notes[self.key],
+                           **sight)
         if finish:
             gate = proj[:, self.g_col: self.g_col + H * dv] if self.gated else None
             rk.attention_finish(raw, self.fv, gate, context, H, dv, ctx)

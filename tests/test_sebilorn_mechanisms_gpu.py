@@ -262,8 +262,9 @@ class _Pages:
 
 def _attend(q, k, v, pages, pieces_list, H, G, dk, dv, dtype, rot, fk, fv, scale, window, keep,
             softcap, gate=None):
-    """Feed the sequences through kv_write_rotated, the attention kernels and attention_finish in
-    the given pieces; returns one [T, H dv] tensor a sequence."""
+    """Feed the sequences in the given pieces through kv_write_rotated, the attention kernels and
+    attention_finish - or, for steps of single tokens at sizes it takes, through the one kernel
+    that does all of it; returns one [T, H dv] tensor a sequence."""
     from distengine_b200.kernels import recurrent as rk
     from distengine_b200.kernels.attention_plan import build_plan
     lens = [x.shape[0] for x in q]
@@ -279,27 +280,37 @@ def _attend(q, k, v, pages, pieces_list, H, G, dk, dv, dtype, rot, fk, fv, scale
                 for s in live]
         proj = torch.cat(rows).to(dtype).to(DEV).contiguous()
         n = proj.shape[0]
-        rk.kv_write_rotated(proj, fk, rot, fv, H, G, dk, dv, pages.k, pages.v, pages.table, True,
-                            ctx)
-        raw = torch.empty(n, H * dv, device=DEV)
-        single = max(pieces) == 1 and rk.chunk_decode_ok(dtype, H, G, dk, dv)
-        if single:
-            rk.chunk_attention_decode(proj, raw, pages.k, pages.v, pages.table, None, None, H, G,
-                                      dk, dv, scale, 0, ctx, window=window, keep_first=keep,
-                                      softcap=softcap)
-        else:
-            # (tiles of 64 rows from 48 rows a portion on, whatever the step's number of blocks)
-            tile = rk.chunk_rows_per_tile(dtype, dk, dv, max(pieces) > 1, max(pieces) * (H // G))
-            plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H // G, G, tile, 0, chunk=0)
-            items = torch.from_numpy(plan.items).to(DEV)
-            rk.chunk_attention(proj, raw, pages.k, pages.v, pages.table, items, None, None, H, G,
-                               dk, dv, scale, 0, ctx, tile_rows=tile, window=window,
-                               keep_first=keep, softcap=softcap)
-        assert int(ctx.status.item()) == 0
-        out = torch.empty(n, H * dv, dtype=dtype, device=DEV)
         gt = None
         if gate is not None:
             gt = torch.cat([gate[s][fed[s]: fed[s] + pieces[s]] for s in live]).to(dtype).to(DEV)
+        out = torch.empty(n, H * dv, dtype=dtype, device=DEV)
+        single = max(pieces) == 1 and rk.chunk_decode_ok(dtype, H, G, dk, dv)
+        if single:
+            # one kernel: rotation, cache write, attention, back-rotation, gate (q stays as it is)
+            before = proj.clone()
+            rk.chunk_attention_decode(proj, out, pages.k, pages.v, pages.table, None, None, H, G,
+                                      dk, dv, scale, 0, ctx, window=window, keep_first=keep,
+                                      softcap=softcap,
+                                      fused=dict(fk=fk, rotary_dim=rot, fv=fv, write_kv=True,
+                                                 gate=gt))
+            assert int(ctx.status.item()) == 0 and torch.equal(proj, before)
+            at = 0
+            for s in live:
+                got[s][fed[s]: fed[s] + pieces[s]] = out[at: at + pieces[s]].float().cpu()
+                at += pieces[s]
+                fed[s] += pieces[s]
+            continue
+        rk.kv_write_rotated(proj, fk, rot, fv, H, G, dk, dv, pages.k, pages.v, pages.table, True,
+                            ctx)
+        raw = torch.empty(n, H * dv, device=DEV)
+        # (tiles of 64 rows from 48 rows a portion on, whatever the step's number of blocks)
+        tile = rk.chunk_rows_per_tile(dtype, dk, dv, max(pieces) > 1, max(pieces) * (H // G))
+        plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H // G, G, tile, 0, chunk=0)
+        items = torch.from_numpy(plan.items).to(DEV)
+        rk.chunk_attention(proj, raw, pages.k, pages.v, pages.table, items, None, None, H, G,
+                           dk, dv, scale, 0, ctx, tile_rows=tile, window=window,
+                           keep_first=keep, softcap=softcap)
+        assert int(ctx.status.item()) == 0
         rk.attention_finish(raw, fv, gt, out, H, dv, ctx)
         at = 0
         for s in live:
